@@ -1,0 +1,202 @@
+/*
+ * trs_cuda.h — C ABI of libtrs_cuda.so, the sm_100a (B200) execution path for
+ * pytorch-rs's data-parallel hot path: fused pointwise chains over strided and
+ * broadcast float32 views, float32 matmul/bmm with fused bias/relu epilogues,
+ * and the reductions and accumulations their autograd backward needs.
+ *
+ * The boundary sits under the reference `Tensor` op methods: the host keeps
+ * shape / stride / broadcast planning and the autograd tape, and calls these
+ * entry points instead of running its element loops when a tensor's storage
+ * lives on a CUDA device.  Each declaration names the reference loop it
+ * replaces (path:line inside the pytorch-rs project).
+ *
+ * Conventions
+ *   - plain C types only; every function returns a trs_status (0 == success);
+ *     nothing throws, aborts or traps.  trs_last_error_message() gives detail.
+ *   - strides and offsets are in ELEMENTS (float32), never negative; a stride
+ *     of 0 marks a broadcast axis.  Shapes follow the reference Tensor
+ *     (src/tensor.rs:212-221).
+ *   - outputs are caller-allocated device buffers; the library never keeps a
+ *     caller pointer past the call except through stream ordering.
+ *   - work is enqueued on the given trs_stream and returns immediately; only
+ *     trs_stream_sync, trs_device_sync and trs_memcpy_d2h (pageable) block.
+ *   - thread-safe per device; callable with the host interpreter lock held.
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point returns TRS_ERR_NO_DEVICE.
+ */
+#ifndef TRS_CUDA_H
+#define TRS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRS_MAX_RANK 8
+#define TRS_MAX_INPUTS 8
+#define TRS_MAX_OUTPUTS 4
+#define TRS_MAX_INSTRS 64
+
+typedef enum trs_status {
+    TRS_OK = 0,
+    TRS_ERR_INVALID_ARGUMENT = 1,
+    TRS_ERR_ALLOCATION_FAILED = 2,   /* maps to TensorError::AllocationFailed (src/tensor_error.rs) */
+    TRS_ERR_CUDA = 3,                /* a CUDA runtime call failed; see trs_last_error_message */
+    TRS_ERR_JIT = 4,                 /* specialising a fused chain failed (compile log in the message) */
+    TRS_ERR_UNSUPPORTED = 5,
+    TRS_ERR_NO_DEVICE = 6,
+    TRS_ERR_DEVICE_STATUS = 7        /* a kernel reported a bounded wait running out or a failed self-check */
+} trs_status;
+
+typedef struct trs_stream_s* trs_stream;   /* a CUDA stream bound to one device */
+typedef struct trs_event_s* trs_event;
+
+/* A strided view of a float32 device buffer (reference: storage + shape + strides + offset,
+ * src/tensor.rs:212-221).  Element (i0..i{rank-1}) lives at base[offset + sum(i_k * stride[k])]. */
+typedef struct trs_operand {
+    void* base;
+    int64_t offset;
+    int32_t rank;
+    int64_t shape[TRS_MAX_RANK];
+    int64_t stride[TRS_MAX_RANK];
+} trs_operand;
+
+/* Fusion IR: a straight-line SSA program over float32 values.  Value k < n_inputs is the
+ * element of input k at the current logical index; value n_inputs + j is the result of
+ * instrs[j].  Unary ops read `a`; binary ops read `a` then `b` (operand order is the
+ * reference closure's order); TRS_OP_CONST yields `imm`. */
+typedef enum trs_op {
+    TRS_OP_CONST = 0,
+    TRS_OP_ADD = 1,        /* a + b      src/tensor.rs:2197  (one IEEE add, never contracted) */
+    TRS_OP_SUB = 2,        /* a - b      src/tensor.rs:2207 */
+    TRS_OP_MUL = 3,        /* a * b      src/tensor.rs:2217 */
+    TRS_OP_DIV = 4,        /* a / b      src/tensor.rs:2245 */
+    TRS_OP_NEG = 5,        /* sign flip  src/tensor.rs:4388 */
+    TRS_OP_RELU = 6,       /* src/tensor.rs:4392-4400: +-0 pass through, NaN -> +0 */
+    TRS_OP_EXP = 7,        /* src/tensor.rs:2398 (libm expf; here within 2 ulp of it) */
+    TRS_OP_RELU_VJP = 8,   /* a = saved input, b = upstream   src/tensor.rs:4422-4432 */
+    TRS_OP_RECIP = 9,      /* 1.0 * (1.0 / a)   src/tensor.rs:2348-2355 */
+    TRS_OP_SQRT = 10,      /* src/tensor.rs:4402-4414 */
+    TRS_OP_SIN = 11,       /* src/tensor.rs:2388 */
+    TRS_OP_COS = 12,       /* used by the sin VJP, src/tensor.rs:3178-3185 */
+    TRS_OP_COPY = 13       /* identity; materialises a view (src/tensor.rs:1805-1838) */
+} trs_op;
+
+typedef struct trs_instr {
+    int32_t op;
+    int32_t a;
+    int32_t b;
+    float imm;
+} trs_instr;
+
+typedef struct trs_program {
+    int32_t n_inputs;
+    int32_t n_instrs;
+    int32_t n_outputs;
+    int32_t outputs[TRS_MAX_OUTPUTS];   /* value index written to output k */
+    trs_instr instrs[TRS_MAX_INSTRS];
+} trs_program;
+
+/* GEMM epilogues fused into the store of C. */
+typedef enum trs_epilogue {
+    TRS_EPI_NONE = 0,
+    TRS_EPI_BIAS = 1,        /* C = A@B + bias[n]                                     */
+    TRS_EPI_BIAS_RELU = 2,   /* C = relu(A@B + bias[n]) ; optional pre-activation copy */
+    TRS_EPI_RELU = 3,
+    TRS_EPI_RELU_VJP = 4     /* C = relu_vjp(aux[m,n], A@B): dZ = relu'(Z) * (dY @ W2^T) */
+} trs_epilogue;
+
+typedef enum trs_gemm_algo {
+    TRS_GEMM_AUTO = 0,
+    TRS_GEMM_SIMT_FP32 = 1,      /* register-tiled FFMA kernel, any strides          */
+    TRS_GEMM_TCGEN05_3XTF32 = 2  /* TMA + tcgen05.mma kind::tf32, 3-product split     */
+} trs_gemm_algo;
+
+/* Batched float32 matmul C[b] = A[b] @ B[b].  All strides in elements.  Replaces
+ * Tensor::matmul (src/tensor.rs:2453-2533, 3889-3966) and extends it to a batch. */
+typedef struct trs_gemm_desc {
+    int64_t batch, m, n, k;
+    const float* a; int64_t a_batch_stride, a_row_stride, a_col_stride;   /* A[b,m,k] */
+    const float* b; int64_t b_batch_stride, b_row_stride, b_col_stride;   /* B[b,k,n] */
+    float* c;       int64_t c_batch_stride, c_row_stride;                 /* C[b,m,n], unit column stride */
+    const float* bias;        /* [n] or NULL */
+    const float* aux;         /* RELU_VJP: saved pre-activation, laid out like C */
+    float* preact;            /* BIAS_RELU: optional copy of A@B+bias, laid out like C, or NULL */
+    int32_t epilogue;         /* trs_epilogue */
+    int32_t algo;             /* trs_gemm_algo */
+} trs_gemm_desc;
+
+/* ---- devices, memory, streams --------------------------------------------------------
+ * New relative to the reference, whose Device has the single variant Cpu (src/device.rs:5-9)
+ * and whose Storage owns a Vec<f32> (src/storage.rs:7-18, 116-134). */
+int32_t trs_device_count(int32_t* count);
+int32_t trs_malloc(int32_t device, size_t bytes, void** ptr);       /* cached blocks; Storage::from_owned */
+int32_t trs_free(int32_t device, void* ptr);                        /* Storage drop */
+int32_t trs_empty_cache(int32_t device);
+int32_t trs_memory_stats(int32_t device, int64_t* bytes_in_use, int64_t* bytes_reserved);
+int32_t trs_malloc_host(size_t bytes, void** ptr);                  /* pinned staging memory */
+int32_t trs_free_host(void* ptr);
+int32_t trs_stream_create(int32_t device, trs_stream* stream);
+int32_t trs_stream_destroy(trs_stream stream);
+int32_t trs_stream_sync(trs_stream stream);
+int32_t trs_stream_device(trs_stream stream, int32_t* device);
+int32_t trs_stream_handle(trs_stream stream, void** cuda_stream);   /* the underlying cudaStream_t */
+int32_t trs_device_sync(int32_t device);
+int32_t trs_event_create(trs_event* event);
+int32_t trs_event_record(trs_event event, trs_stream stream);
+int32_t trs_event_sync(trs_event event);
+int32_t trs_event_elapsed_ms(trs_event start, trs_event stop, float* ms);
+int32_t trs_event_destroy(trs_event event);
+int32_t trs_stream_wait_event(trs_stream stream, trs_event event);
+/* Tensor ingestion/egress (src/python.rs:10329-10403 flatten_buffer; 4031-4052 numpy_array_copy). */
+int32_t trs_memcpy_h2d(void* dst, const void* src, size_t bytes, trs_stream stream);
+int32_t trs_memcpy_d2h(void* dst, const void* src, size_t bytes, trs_stream stream);
+int32_t trs_memcpy_d2d(void* dst, const void* src, size_t bytes, trs_stream stream);
+
+/* ---- pointwise -------------------------------------------------------------------------
+ * One kernel for a whole recorded chain.  Replaces zip_map / map_scalar / unary_map and their
+ * materialize_* loops (src/tensor.rs:2535-2789, 1805-1838, 3376-3599) and the pointwise VJP
+ * arms of apply_grad_fn (src/tensor.rs:3014-3029, 3161-3176).  Inputs are broadcast to the
+ * outputs' shape by stride-0 axes; all outputs share one shape; outputs must not overlap
+ * inputs.  The chain is specialised (compiled once per program + layout class, then cached). */
+int32_t trs_pointwise(const trs_program* program, const trs_operand* inputs, const trs_operand* outputs,
+                      trs_stream stream);
+/* Compile (without launching) the kernel trs_pointwise would use; needs no GPU. Writes the
+ * chosen kernel class ("vector", "tiled") to `klass` when non-NULL (at least 16 bytes). */
+int32_t trs_pointwise_prepare(const trs_program* program, const trs_operand* inputs, const trs_operand* outputs,
+                              char* klass);
+/* filled_storage (src/tensor.rs:4434-4442): Sum VJP fill, zeros/ones/full. */
+int32_t trs_fill_f32(float* dst, int64_t count, float value, trs_stream stream);
+/* accumulate_shared_gradient (src/storage.rs:85-100) and add_gradient (src/tensor.rs:3302-3317):
+ * dst[i] += src[i]. */
+int32_t trs_accumulate_f32(float* dst, const float* src, int64_t count, trs_stream stream);
+
+/* ---- reductions ----------------------------------------------------------------------------
+ * Tensor::sum (src/tensor.rs:2413-2431): all elements of a view -> one float at *out (device).
+ * Deterministic two-stage tree; differs from the reference's sequential order by rounding only. */
+int32_t trs_reduce_sum_f32(const trs_operand* input, float* out, trs_stream stream);
+/* GradientAccumulator (src/tensor.rs:3204-3228): out[j] = sum over rows r of in[r*cols + j]
+ * (un-broadcast of a leading axis, e.g. db1 = sum_rows dZ), or with by_rows != 0
+ * out[r] = sum over j of in[r*cols + j] (un-broadcast of a trailing axis). Deterministic. */
+int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, int32_t by_rows, float* out,
+                                trs_stream stream);
+
+/* ---- matmul ----------------------------------------------------------------------------------
+ * Honours float32 matmul precision "highest" (python/torch_rs/__init__.py:81-85): either exact
+ * FP32 FMA accumulation or the 3xTF32 error-compensated split with FP32 accumulation. */
+int32_t trs_matmul_f32(const trs_gemm_desc* desc, trs_stream stream);
+/* Which algorithm TRS_GEMM_AUTO resolves to for this descriptor (no launch). */
+int32_t trs_matmul_select_algo(const trs_gemm_desc* desc, int32_t* algo);
+
+/* ---- diagnostics -------------------------------------------------------------------------------- */
+const char* trs_status_string(int32_t status);
+const char* trs_last_error_message(void);          /* thread-local, valid until the next failing call */
+int64_t trs_kernel_launch_count(void);             /* kernels launched by this library since load */
+int32_t trs_jit_cache_size(int32_t* entries);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRS_CUDA_H */

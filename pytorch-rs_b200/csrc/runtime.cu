@@ -1,0 +1,280 @@
+// Devices, cached device memory, pinned host memory, streams, events and copies.
+//
+// The reference owns host Vec<f32> buffers (src/storage.rs:7-18); here a Storage is a block of
+// HBM handed out by a per-device size-bucketed cache so that the per-op fresh output allocation
+// the reference performs (from_owned_parts, src/tensor.rs:432-450) costs no cudaMalloc after
+// warm-up.  Freed blocks are reused in stream order on the library's streams; callers that mix
+// several streams on one device order them with events before freeing.
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+
+namespace trs {
+thread_local std::string g_last_error;
+std::atomic<int64_t> g_launches{0};
+
+namespace {
+constexpr int kMaxDevices = 16;
+struct DeviceCache {
+    std::mutex mu;
+    std::multimap<size_t, void*> free_blocks;          // rounded size -> block
+    std::unordered_map<void*, size_t> live;            // block -> rounded size
+    int64_t in_use = 0, reserved = 0;
+    int sms = 0;
+};
+DeviceCache g_cache[kMaxDevices];
+
+size_t round_size(size_t bytes) {
+    if (bytes == 0) bytes = 1;
+    if (bytes <= (1u << 20)) return (bytes + 511) & ~size_t(511);
+    return (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);   // 2 MiB granularity above 1 MiB
+}
+
+void release_all(DeviceCache& c) {
+    for (auto& kv : c.free_blocks) {
+        cudaFree(kv.second);
+        c.reserved -= (int64_t)kv.first;
+    }
+    c.free_blocks.clear();
+}
+}  // namespace
+
+int32_t check_stream(trs_stream s) {
+    if (!s) return fail(TRS_ERR_INVALID_ARGUMENT, "stream must not be NULL (use trs_stream_create)");
+    return TRS_OK;
+}
+
+int sm_count(int device) {
+    DeviceCache& c = g_cache[device];
+    if (c.sms == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) v = 148;
+        c.sms = v;
+    }
+    return c.sms;
+}
+}  // namespace trs
+
+using namespace trs;
+
+extern "C" {
+
+int32_t trs_device_count(int32_t* count) {
+    if (!count) return fail(TRS_ERR_INVALID_ARGUMENT, "count is NULL");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *count = 0;
+        cudaGetLastError();
+        return cuda_fail(e, "cudaGetDeviceCount");
+    }
+    *count = n;
+    return TRS_OK;
+}
+
+int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) {
+    if (!ptr || device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad trs_malloc arguments");
+    *ptr = nullptr;
+    DeviceCache& c = g_cache[device];
+    size_t rounded = round_size(bytes);
+    std::lock_guard<std::mutex> lock(c.mu);
+    auto it = c.free_blocks.lower_bound(rounded);
+    // Reuse only a block that wastes at most 1/8 of itself, so large blocks stay available for large requests.
+    if (it != c.free_blocks.end() && it->first <= rounded + rounded / 8) {
+        *ptr = it->second;
+        c.live[*ptr] = it->first;
+        c.in_use += (int64_t)it->first;
+        c.free_blocks.erase(it);
+        return TRS_OK;
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, rounded);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        release_all(c);                      // give cached blocks back and retry once
+        e = cudaMalloc(&p, rounded);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(e, "cudaMalloc");
+    }
+    c.live[p] = rounded;
+    c.in_use += (int64_t)rounded;
+    c.reserved += (int64_t)rounded;
+    *ptr = p;
+    return TRS_OK;
+}
+
+int32_t trs_free(int32_t device, void* ptr) {
+    if (!ptr) return TRS_OK;
+    if (device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device");
+    DeviceCache& c = g_cache[device];
+    std::lock_guard<std::mutex> lock(c.mu);
+    auto it = c.live.find(ptr);
+    if (it == c.live.end()) return fail(TRS_ERR_INVALID_ARGUMENT, "pointer was not allocated by trs_malloc on device %d", device);
+    c.in_use -= (int64_t)it->second;
+    c.free_blocks.emplace(it->second, ptr);
+    c.live.erase(it);
+    return TRS_OK;
+}
+
+int32_t trs_empty_cache(int32_t device) {
+    if (device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device");
+    DeviceCache& c = g_cache[device];
+    std::lock_guard<std::mutex> lock(c.mu);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
+    cudaDeviceSynchronize();
+    release_all(c);
+    return TRS_OK;
+}
+
+int32_t trs_memory_stats(int32_t device, int64_t* bytes_in_use, int64_t* bytes_reserved) {
+    if (device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device");
+    DeviceCache& c = g_cache[device];
+    std::lock_guard<std::mutex> lock(c.mu);
+    if (bytes_in_use) *bytes_in_use = c.in_use;
+    if (bytes_reserved) *bytes_reserved = c.reserved;
+    return TRS_OK;
+}
+
+int32_t trs_malloc_host(size_t bytes, void** ptr) {
+    if (!ptr) return fail(TRS_ERR_INVALID_ARGUMENT, "ptr is NULL");
+    TRS_CUDA(cudaMallocHost(ptr, bytes ? bytes : 1));
+    return TRS_OK;
+}
+
+int32_t trs_free_host(void* ptr) {
+    if (ptr) TRS_CUDA(cudaFreeHost(ptr));
+    return TRS_OK;
+}
+
+int32_t trs_stream_create(int32_t device, trs_stream* stream) {
+    if (!stream) return fail(TRS_ERR_INVALID_ARGUMENT, "stream is NULL");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
+    cudaStream_t s;
+    TRS_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = new trs_stream_s{device, s};
+    return TRS_OK;
+}
+
+int32_t trs_stream_destroy(trs_stream stream) {
+    if (!stream) return TRS_OK;
+    DeviceGuard guard(stream->device);
+    cudaStreamSynchronize(stream->stream);
+    cudaStreamDestroy(stream->stream);
+    delete stream;
+    return TRS_OK;
+}
+
+int32_t trs_stream_sync(trs_stream stream) {
+    TRS_TRY(check_stream(stream));
+    TRS_CUDA(cudaStreamSynchronize(stream->stream));
+    return TRS_OK;
+}
+
+int32_t trs_stream_device(trs_stream stream, int32_t* device) {
+    TRS_TRY(check_stream(stream));
+    if (device) *device = stream->device;
+    return TRS_OK;
+}
+
+int32_t trs_stream_handle(trs_stream stream, void** cuda_stream) {
+    TRS_TRY(check_stream(stream));
+    if (cuda_stream) *cuda_stream = (void*)stream->stream;
+    return TRS_OK;
+}
+
+int32_t trs_device_sync(int32_t device) {
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
+    TRS_CUDA(cudaDeviceSynchronize());
+    return TRS_OK;
+}
+
+int32_t trs_event_create(trs_event* event) {
+    if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    cudaEvent_t e;
+    TRS_CUDA(cudaEventCreate(&e));
+    *event = new trs_event_s{e};
+    return TRS_OK;
+}
+
+int32_t trs_event_record(trs_event event, trs_stream stream) {
+    TRS_TRY(check_stream(stream));
+    if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    DeviceGuard guard(stream->device);
+    TRS_CUDA(cudaEventRecord(event->event, stream->stream));
+    return TRS_OK;
+}
+
+int32_t trs_event_sync(trs_event event) {
+    if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    TRS_CUDA(cudaEventSynchronize(event->event));
+    return TRS_OK;
+}
+
+int32_t trs_event_elapsed_ms(trs_event start, trs_event stop, float* ms) {
+    if (!start || !stop || !ms) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL argument");
+    TRS_CUDA(cudaEventElapsedTime(ms, start->event, stop->event));
+    return TRS_OK;
+}
+
+int32_t trs_event_destroy(trs_event event) {
+    if (!event) return TRS_OK;
+    cudaEventDestroy(event->event);
+    delete event;
+    return TRS_OK;
+}
+
+int32_t trs_stream_wait_event(trs_stream stream, trs_event event) {
+    TRS_TRY(check_stream(stream));
+    if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    DeviceGuard guard(stream->device);
+    TRS_CUDA(cudaStreamWaitEvent(stream->stream, event->event, 0));
+    return TRS_OK;
+}
+
+static int32_t copy(void* dst, const void* src, size_t bytes, trs_stream stream, cudaMemcpyKind kind) {
+    TRS_TRY(check_stream(stream));
+    if (bytes == 0) return TRS_OK;
+    if (!dst || !src) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL copy pointer");
+    DeviceGuard guard(stream->device);
+    TRS_CUDA(cudaMemcpyAsync(dst, src, bytes, kind, stream->stream));
+    return TRS_OK;
+}
+
+int32_t trs_memcpy_h2d(void* dst, const void* src, size_t bytes, trs_stream stream) {
+    return copy(dst, src, bytes, stream, cudaMemcpyHostToDevice);
+}
+int32_t trs_memcpy_d2h(void* dst, const void* src, size_t bytes, trs_stream stream) {
+    return copy(dst, src, bytes, stream, cudaMemcpyDeviceToHost);
+}
+int32_t trs_memcpy_d2d(void* dst, const void* src, size_t bytes, trs_stream stream) {
+    return copy(dst, src, bytes, stream, cudaMemcpyDeviceToDevice);
+}
+
+const char* trs_status_string(int32_t status) {
+    switch (status) {
+        case TRS_OK: return "ok";
+        case TRS_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case TRS_ERR_ALLOCATION_FAILED: return "allocation failed";
+        case TRS_ERR_CUDA: return "CUDA error";
+        case TRS_ERR_JIT: return "kernel specialisation failed";
+        case TRS_ERR_UNSUPPORTED: return "unsupported";
+        case TRS_ERR_NO_DEVICE: return "no CUDA device";
+        case TRS_ERR_DEVICE_STATUS: return "device-side status error";
+        default: return "unknown status";
+    }
+}
+
+const char* trs_last_error_message(void) { return g_last_error.c_str(); }
+int64_t trs_kernel_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"
