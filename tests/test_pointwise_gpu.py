@@ -1,0 +1,171 @@
+"""GPU parity of fused pointwise chains, called through the C ABI, against the CPU checker.
+
+add / sub / mul / relu / relu-VJP: bit-exact on every non-NaN lane, NaN-ness equal.
+exp: at most 2 ulp from the checker's libm expf (the tolerance the path states).
+Layout cases mirror the reference's own (src/tensor.rs:4946-5226, tests/test_operation_chains_reference.py:47-58).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import ref
+from oracle.ref import RefTensor
+from tests.abi_harness import assert_bits_equal, run_pointwise
+
+pytestmark = pytest.mark.gpu
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+
+
+def hexf(items):
+    return np.array([int(h, 16) for h in items], dtype=np.uint32).view(np.float32)
+
+
+def rnd(seed, *shape):
+    return np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
+
+
+@pytest.mark.parametrize("shape", [(4096,), (257, 129), (3, 5, 7), (1,), (64, 1024), (5, 4, 3, 2, 3)])
+def test_relu_add_contiguous(shape):
+    x = RefTensor.from_numpy(np.random.default_rng(0).uniform(-1, 1, shape).astype(np.float32))
+    y = RefTensor.from_numpy(np.random.default_rng(1).uniform(-1, 1, shape).astype(np.float32))
+    expected = (x + y).relu()
+    (got,) = run_pointwise([("add", 0, 1, 0), ("relu", 2, 0, 0)], [3], [x, y], [(expected.shape, expected.strides)])
+    assert_bits_equal(got, expected.storage, f"relu(x+y) {shape}")
+
+
+@pytest.mark.parametrize("rows,cols", [(192, 320), (33, 7), (128, 128), (1, 9), (8, 1024)])
+def test_transposed_view_broadcast_exp_chain(rows, cols):
+    # exp(2.0 * relu(x.mT + b)) - x.mT : every op keeps the view's strides, so one streaming kernel.
+    xs = RefTensor.from_numpy(rnd(0, rows, cols))
+    b = RefTensor.from_numpy((0.1 * rnd(1, rows)).astype(np.float32))
+    xt = xs.mT
+    expected = (2.0 * (xt + b).relu()).exp() - xt
+    if rows > 1 and cols > 1:
+        assert expected.strides == xt.strides      # tests/test_transpose.py:244-259 in the reference
+    prog = [("add", 0, 1, 0), ("relu", 2, 0, 0), ("const", 0, 0, 2.0), ("mul", 3, 4, 0), ("exp", 5, 0, 0), ("sub", 6, 0, 0)]
+    (got,) = run_pointwise(prog, [7], [xt, b], [(expected.shape, expected.strides)])
+    ulp = ref.ulp_distance(got, expected.storage)
+    assert ulp.max() <= 2, f"max ulp {ulp.max()}"
+
+
+@pytest.mark.parametrize("rows,cols", [(100, 70), (64, 64), (257, 33), (8, 8), (1000, 24)])
+def test_transposed_operand_against_contiguous_uses_staged_tiles(rows, cols):
+    xs = RefTensor.from_numpy(rnd(2, cols, rows))
+    y = RefTensor.from_numpy(rnd(3, rows, cols))
+    xt = xs.mT
+    for left, right in ((xt, y), (y, xt)):
+        expected = left * right + left
+        prog = [("mul", 0, 1, 0), ("add", 2, 0, 0)]
+        (got,) = run_pointwise(prog, [3], [left, right], [(expected.shape, expected.strides)])
+        assert_bits_equal(got, (left * right + left).storage, f"{rows}x{cols}")
+
+
+def test_rank3_permuted_offset_and_strided_views():
+    base = RefTensor.from_numpy(rnd(4, 2, 6, 5, 7))
+    view = base.select0(1).permute([2, 0, 1])            # offset view, permuted: shape [7,6,5]
+    other = RefTensor.from_numpy(rnd(5, 6, 1))             # broadcast [6,1] against [7,6,5]
+    expected = (view - other) * view
+    (got,) = run_pointwise([("sub", 0, 1, 0), ("mul", 2, 0, 0)], [3], [view, other], [(expected.shape, expected.strides)])
+    assert_bits_equal(got, expected.storage, "permuted offset view")
+    # a non-dense input (every second column), which only the ABI can express
+    wide = RefTensor(rnd(6, 40 * 50), [40, 25], [50, 2], offset=1)
+    exp_t = wide.relu()
+    (got,) = run_pointwise([("relu", 0, 0, 0)], [1], [wide], [(exp_t.shape, exp_t.strides)])
+    assert_bits_equal(got, exp_t.storage, "strided slice")
+
+
+def test_broadcast_mixed_ranks_golden():
+    g = GOLD["broadcast_arithmetic"]
+    left = RefTensor(np.array(g["left"]["values"], dtype=np.float32), g["left"]["shape"])
+    right = RefTensor(np.array(g["right"]["values"], dtype=np.float32), g["right"]["shape"])
+    for op in ("add", "sub", "mul", "div"):
+        expected = left.binary(op, right)
+        (got,) = run_pointwise([(op, 0, 1, 0)], [2], [left, right], [(expected.shape, expected.strides)])
+        assert got.tolist() == g[op]
+
+
+def test_relu_golden_bits_through_offset_and_transposed_views():
+    g = GOLD["relu_bits"]
+    storage = np.concatenate([np.ones(12, dtype=np.float32), hexf(g["input"])])
+    view = RefTensor(storage, g["base_shape"]).select0(1)
+    for v, key in ((view, "expected"), (view.transpose(0, 1), "transposed_expected")):
+        expected = v.relu()
+        (got,) = run_pointwise([("relu", 0, 0, 0)], [1], [v], [(expected.shape, expected.strides)])
+        logical = RefTensor(got, expected.shape, expected.strides).logical()
+        assert [f"{b:08x}" for b in logical.reshape(-1).view(np.uint32)] == g[key]
+
+
+def test_relu_vjp_golden_bits():
+    g = GOLD["relu_vjp_bits"]
+    x, w = RefTensor(hexf(g["input"]), [12]), RefTensor(hexf(g["weights"]), [12])
+    ones = RefTensor(np.ones(12, dtype=np.float32), [12])
+    # upstream = 1 * weights (Multiply VJP), then relu VJP against the saved input
+    (got,) = run_pointwise([("mul", 2, 1, 0), ("relu_vjp", 0, 3, 0)], [4], [x, w, ones], [([12], [1])])
+    assert [f"{b:08x}" for b in got.view(np.uint32)] == g["expected_gradient"]
+
+
+def test_exp_goldens_and_specials():
+    g = GOLD["exp_ordinary"]
+    x = RefTensor(np.array(g["input"], dtype=np.float32), [2, 2, 3])
+    (got,) = run_pointwise([("exp", 0, 0, 0)], [1], [x], [([2, 2, 3], [6, 3, 1])])
+    atol = float(hexf([g["atol_bits"]])[0])
+    for a, e in zip(got, g["expected"]):
+        assert abs(float(a) - e) <= atol + g["rtol"] * abs(e)
+    s = GOLD["exp_special"]
+    xs = RefTensor(hexf(s["input_bits"]), [11])
+    (got,) = run_pointwise([("exp", 0, 0, 0)], [1], [xs], [([11], [1])])
+    expected = xs.exp().storage
+    assert ref.ulp_distance(got, expected).max() <= 2
+    b = got.view(np.uint32)
+    assert all(v == 0x3F800000 for v in b[:4])
+    assert 0 < b[4] < 0x00800000 and b[5] == 0 and b[7] == 0x7F800000 and np.isnan(got[8])
+    assert b[9] == 0x7F800000 and b[10] == 0
+
+
+def test_exp_two_ulp_over_wide_range():
+    x = RefTensor.from_numpy(np.random.default_rng(11).uniform(-104, 89, 1 << 20).astype(np.float32))
+    (got,) = run_pointwise([("exp", 0, 0, 0)], [1], [x], [(x.shape, x.strides)])
+    assert ref.ulp_distance(got, x.exp().storage).max() <= 2
+
+
+def test_scalar_forms_and_rank_zero():
+    x = RefTensor.from_numpy(rnd(8, 37, 5))
+    expected = (1.5 - (x * 3.0 + 0.25) / 7.0)
+    prog = [("const", 0, 0, 3.0), ("mul", 0, 1, 0), ("const", 0, 0, 0.25), ("add", 2, 3, 0), ("const", 0, 0, 7.0),
+            ("div", 4, 5, 0), ("const", 0, 0, 1.5), ("sub", 7, 6, 0)]
+    (got,) = run_pointwise(prog, [8], [x], [(expected.shape, expected.strides)])
+    assert_bits_equal(got, expected.storage, "scalar chain")
+    recip = 2.0 / x
+    (got,) = run_pointwise([("reciprocal", 0, 0, 0), ("const", 0, 0, 2.0), ("mul", 2, 1, 0)], [3], [x], [(x.shape, x.strides)])
+    # scalar_div is scalar * recip(value) (src/tensor.rs:2363); reciprocal op is 1.0 * recip
+    assert_bits_equal(got, recip.storage, "reflected division")
+    s = RefTensor(np.array([-0.0], dtype=np.float32), [])
+    (got,) = run_pointwise([("relu", 0, 0, 0)], [1], [s], [([], [])])
+    assert got.view(np.uint32)[0] == 0x80000000
+
+
+def test_empty_and_multi_output():
+    e = RefTensor(np.zeros(0, dtype=np.float32), [2, 0, 3])
+    (got,) = run_pointwise([("relu", 0, 0, 0)], [1], [e], [([2, 0, 3], [3, 3, 1])])
+    assert got.size == 0
+    x, y = RefTensor.from_numpy(rnd(9, 130, 66)), RefTensor.from_numpy(rnd(10, 130, 66))
+    pre = x + y
+    act = pre.relu()
+    got_pre, got_act = run_pointwise([("add", 0, 1, 0), ("relu", 2, 0, 0)], [2, 3], [x, y],
+                                     [(pre.shape, pre.strides), (act.shape, act.strides)])
+    assert_bits_equal(got_pre, pre.storage, "pre-activation output")
+    assert_bits_equal(got_act, act.storage, "activation output")
+
+
+def test_special_values_bitwise():
+    specials = hexf(["80000000", "00000000", "00000001", "80000001", "7f800000", "ff800000", "7fc00000", "3f800000",
+                     "7f7fffff", "ff7fffff", "00800000", "80800000"])
+    a = np.repeat(specials, len(specials))
+    b = np.tile(specials, len(specials))
+    x, y = RefTensor(a, [a.size]), RefTensor(b, [b.size])
+    for op in ("add", "sub", "mul"):
+        expected = x.binary(op, y)
+        (got,) = run_pointwise([(op, 0, 1, 0)], [2], [x, y], [(expected.shape, expected.strides)])
+        assert_bits_equal(got, expected.storage, op)
