@@ -1,0 +1,204 @@
+// Tensor creation, views, op recording and egress for CUDA tensors.
+//
+// Pointwise ops do not run when called: each returns a tensor whose storage is a pending
+// expression node carrying the already planned shape and strides (which depend on metadata
+// only, so .shape/.stride() answer at once).  fuse.cpp lowers a pending expression to the
+// fusion IR of the C ABI and runs it as one kernel when a value is needed.
+#include "engine.h"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+
+namespace trsh {
+
+std::recursive_mutex g_engine_mu;
+
+namespace {
+thread_local int t_no_grad_depth = 0;
+std::map<int, trs_stream> g_streams;
+}  // namespace
+
+bool grad_enabled() { return t_no_grad_depth == 0; }   // src/grad_mode.rs:5-56
+void set_grad_enabled(bool on) {
+    if (on) { if (t_no_grad_depth > 0) --t_no_grad_depth; }
+    else ++t_no_grad_depth;
+}
+
+void check_cuda(int32_t status, const char* what) {
+    if (status == TRS_OK) return;
+    std::string msg = std::string(what) + ": " + trs_status_string(status) + ": " + trs_last_error_message();
+    throw Error(status == TRS_ERR_ALLOCATION_FAILED ? ErrKind::AllocationFailed : ErrKind::Device, msg);
+}
+
+trs_stream stream_for(int device) {
+    auto it = g_streams.find(device);
+    if (it != g_streams.end()) return it->second;
+    trs_stream s = nullptr;
+    check_cuda(trs_stream_create(device, &s), "creating the device stream");
+    g_streams[device] = s;
+    return s;
+}
+
+Storage::~Storage() {
+    if (ptr) trs_free(device, ptr);
+}
+
+void sync(int device) { check_cuda(trs_stream_sync(stream_for(device)), "stream sync"); }
+
+static std::shared_ptr<Storage> alloc_storage(i64 count, int device) {
+    auto st = std::make_shared<Storage>();
+    st->device = device;
+    st->count = count;
+    void* p = nullptr;
+    int32_t s = trs_malloc(device, (size_t)std::max<i64>(count, 1) * sizeof(float), &p);
+    if (s == TRS_ERR_ALLOCATION_FAILED)
+        throw Error(ErrKind::AllocationFailed, "failed to allocate storage for " + std::to_string(count) + " elements");
+    check_cuda(s, "device allocation");
+    st->ptr = (float*)p;
+    return st;
+}
+
+TensorP make_tensor(View v) {
+    auto t = std::make_shared<Tensor>();
+    t->numel = element_count(v.shape);
+    t->v = std::move(v);
+    return t;
+}
+
+TensorP from_host(const float* data, const Shape& shape, int device) {
+    for (i64 d : shape) if (d < 0) throw Error(ErrKind::InvalidArgument, "negative dimension");
+    const i64 n = element_count(shape);
+    auto st = alloc_storage(n, device);
+    if (n > 0) {
+        trs_stream s = stream_for(device);
+        check_cuda(trs_memcpy_h2d(st->ptr, data, (size_t)n * sizeof(float), s), "host to device copy");
+        check_cuda(trs_stream_sync(s), "host to device copy");   // the source is pageable caller memory
+    }
+    return make_tensor(View{st, shape, contiguous_strides(shape), 0});
+}
+
+TensorP full(const Shape& shape, float value, int device) {
+    const i64 n = element_count(shape);
+    auto st = alloc_storage(n, device);
+    if (n > 0) check_cuda(trs_fill_f32(st->ptr, n, value, stream_for(device)), "fill");
+    return make_tensor(View{st, shape, contiguous_strides(shape), 0});
+}
+
+TensorP zeros_like_shape(const Shape& shape, int device) { return full(shape, 0.0f, device); }
+
+// ---- views (metadata only; src/tensor.rs:1082-1215, 1850-1973) -----------------------------------
+
+TensorP detach(const TensorP& t) {
+    auto out = make_tensor(t->v);
+    return out;
+}
+
+static i64 wrap_dim(i64 dim, size_t rank) {
+    // normalize_transpose_dimension (src/tensor.rs:3793-3813); message src/tensor_error.rs:252-263
+    const i64 r = (i64)std::max<size_t>(rank, 1);
+    if (dim < -r || dim >= r)
+        throw Error(ErrKind::DimensionOutOfRange, "Dimension out of range (expected to be in range of [-" + std::to_string(r) + ", " +
+                                                      std::to_string(r - 1) + "], but got " + std::to_string(dim) + ")");
+    if (rank == 0) return 0;
+    return dim < 0 ? dim + r : dim;
+}
+
+TensorP transpose(const TensorP& t, i64 d0, i64 d1) {
+    const size_t rank = t->v.shape.size();
+    const i64 a0 = wrap_dim(d0, rank), a1 = wrap_dim(d1, rank);
+    std::vector<i64> dims(rank);
+    for (size_t i = 0; i < rank; ++i) dims[i] = (i64)i;
+    if (rank) std::swap(dims[a0], dims[a1]);
+    return permute(t, dims, 1);
+}
+
+TensorP matrix_transpose(const TensorP& t) {
+    const size_t rank = t->v.shape.size();
+    if (rank == 1)
+        throw Error(ErrKind::MatrixTransposeRequiresMatrix, "tensor.mT is only supported on matrices or batches of matrices. Got 1-D tensor.");
+    if (rank == 0) return permute(t, {}, 1);
+    return transpose(t, -2, -1);
+}
+
+TensorP reverse_dims(const TensorP& t) {
+    std::vector<i64> dims(t->v.shape.size());
+    for (size_t i = 0; i < dims.size(); ++i) dims[i] = (i64)(dims.size() - 1 - i);
+    return permute(t, dims, 0);
+}
+
+// ---- op recording -------------------------------------------------------------------------------
+
+static bool is_identity_view_of_pending(const View& v) {
+    const Storage& st = *v.st;
+    return st.node && v.offset == 0 && v.shape == st.node->shape && v.strides == st.node->strides;
+}
+
+TensorP pointwise_node(int op, float imm, std::vector<View> args, const Shape& shape, const Shape& strides, int device) {
+    auto node = std::make_shared<Node>();
+    node->op = op;
+    node->imm = imm;
+    node->shape = shape;
+    node->strides = strides;
+    int instrs = 1, leaves = 0;
+    for (View& a : args) {
+        if (a.st->device != device)
+            throw Error(ErrKind::DeviceMismatch, "Expected all tensors to be on the same device, but found at least two devices, cuda:" +
+                                                     std::to_string(device) + " and cuda:" + std::to_string(a.st->device) + "!");
+        if (a.st->node) {
+            // A pending operand fuses only when it is read element for element (identity view,
+            // same logical shape); otherwise its values are needed in memory first.
+            if (is_identity_view_of_pending(a) && a.shape == shape && a.st->node->n_instr + instrs <= 40 &&
+                a.st->node->n_leaf + leaves <= TRS_MAX_INPUTS - 2) {
+                instrs += a.st->node->n_instr;
+                leaves += a.st->node->n_leaf;
+                continue;
+            }
+            materialize(a.st);
+        }
+        leaves += 1;
+    }
+    node->n_instr = instrs;
+    node->n_leaf = leaves;
+    node->args = std::move(args);
+    auto st = std::make_shared<Storage>();
+    st->device = device;
+    st->count = element_count(shape);
+    st->node = node;
+    return make_tensor(View{st, shape, strides, 0});
+}
+
+void to_host(const Tensor& t, float* out) {
+    if (t.numel == 0) return;
+    const int device = t.device();
+    materialize(t.v.st);
+    trs_stream s = stream_for(device);
+    if (layout_is_contiguous(t.v.shape, t.v.strides)) {
+        check_cuda(trs_memcpy_d2h(out, t.v.st->ptr + t.v.offset, (size_t)t.numel * 4, s), "device to host copy");
+        check_cuda(trs_stream_sync(s), "device to host copy");
+        return;
+    }
+    // Gather into logical order on the device (one fused copy), then read back.
+    TensorP packed = pointwise_node(TRS_OP_COPY, 0.f, {t.v}, t.v.shape, contiguous_strides(t.v.shape), device);
+    materialize(packed->v.st);
+    check_cuda(trs_memcpy_d2h(out, packed->v.st->ptr, (size_t)t.numel * 4, s), "device to host copy");
+    check_cuda(trs_stream_sync(s), "device to host copy");
+}
+
+float item(const Tensor& t) {
+    // src/tensor.rs:2438-2445
+    if (t.numel != 1) throw Error(ErrKind::ItemRequiresOneElement, "item requires one element, got " + std::to_string(t.numel));
+    materialize(t.v.st);
+    float v = 0.f;
+    trs_stream s = stream_for(t.device());
+    check_cuda(trs_memcpy_d2h(&v, t.v.st->ptr + t.v.offset, 4, s), "device to host copy");
+    check_cuda(trs_stream_sync(s), "device to host copy");
+    return v;
+}
+
+TensorP contiguous(const TensorP& t) {
+    if (layout_is_contiguous(t->v.shape, t->v.strides)) return t;
+    return pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, contiguous_strides(t->v.shape), t->device());
+}
+
+}  // namespace trsh

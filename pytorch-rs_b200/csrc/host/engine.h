@@ -1,0 +1,151 @@
+// Host engine: the C++ stand-in for the reference's Rust core (src/tensor.rs, src/storage.rs,
+// src/autograd_node.rs) for tensors whose storage lives on a CUDA device.  It keeps the
+// reference's metadata rules (shape / stride / broadcast planning, view construction, autograd
+// tape) on the host and replaces its element loops by calls into the C ABI of libtrs_cuda.so.
+// It links against nothing but that C ABI, exactly as the Rust crate would.
+#pragma once
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../../include/trs_cuda.h"
+
+namespace trsh {
+
+using i64 = int64_t;
+using Shape = std::vector<i64>;
+
+// Mirrors the TensorError variants the hot path can raise (src/tensor_error.rs:7-108); the
+// messages are the reference's Display strings (src/tensor_error.rs:110-393).
+enum class ErrKind : int {
+    None = 0,
+    ShapeMismatch = 1,
+    MatmulRequiresMatrices = 2,
+    MatmulInnerDimensionMismatch = 3,
+    ItemRequiresOneElement = 4,
+    IndexOutOfBounds = 5,
+    DimensionOutOfRange = 6,
+    PermutationRankMismatch = 7,
+    PermutationDimensionOutOfRange = 8,
+    DuplicatePermutationDimension = 9,
+    MatrixTransposeRequiresMatrix = 10,
+    StrideCalculationOverflow = 11,
+    ElementCountOverflow = 12,
+    AllocationFailed = 13,
+    BackwardRequiresScalar = 14,
+    DoesNotRequireGrad = 15,
+    BackwardGraphFreed = 16,
+    InvalidScalarIndex = 17,
+    DeviceMismatch = 18,
+    Device = 19,            // a libtrs_cuda call failed (no device, CUDA error, ...)
+    InvalidArgument = 20,
+    ShapeDataMismatch = 21,
+};
+
+struct Error : std::runtime_error {
+    ErrKind kind;
+    Error(ErrKind k, const std::string& m) : std::runtime_error(m), kind(k) {}
+};
+
+struct Node;
+
+// Device buffer or a pending (not yet computed) pointwise result.  Immutable once filled, except
+// a leaf gradient, which is accumulated in place (src/storage.rs:85-100).
+struct Storage {
+    int device = 0;
+    float* ptr = nullptr;
+    i64 count = 0;
+    std::shared_ptr<Node> node;   // non-null while the values are still an unevaluated expression
+    ~Storage();
+};
+
+struct View {
+    std::shared_ptr<Storage> st;
+    Shape shape, strides;
+    i64 offset = 0;
+};
+
+constexpr int OP_MATMUL = 100;   // lazy matmul node (so bias / relu / relu-VJP can fuse as epilogue)
+
+struct Node {
+    int op = 0;                  // trs_op or OP_MATMUL
+    float imm = 0.f;
+    std::vector<View> args;
+    Shape shape, strides;        // layout of the value this node produces (offset 0)
+    int n_instr = 1, n_leaf = 0; // conservative size of the pending expression under this node
+};
+
+struct GradFn;
+struct Tensor;
+
+struct AutogradMeta {
+    bool leaf = false;
+    std::shared_ptr<GradFn> grad_fn;          // non-leaf; reset when the graph is freed
+    bool freed = false;
+    std::shared_ptr<Tensor> grad;             // leaf: accumulated gradient (contiguous)
+    Shape leaf_shape;
+    int device = 0;
+};
+
+struct Tensor {
+    View v;
+    i64 numel = 0;
+    std::shared_ptr<AutogradMeta> meta;
+    bool view_requires_grad = false;
+    bool requires_grad() const { return meta != nullptr || view_requires_grad; }
+    bool is_leaf() const { return !meta || meta->leaf; }
+    int device() const { return v.st->device; }
+};
+using TensorP = std::shared_ptr<Tensor>;
+
+// ---- layout rules (layout.cpp) -----------------------------------------------------------------
+i64 element_count(const Shape& shape);
+Shape contiguous_strides(const Shape& shape);
+bool layout_is_contiguous(const Shape& shape, const Shape& strides);
+bool is_non_overlapping_and_dense(const Shape& shape, const Shape& strides);
+Shape unary_output_strides(const Shape& shape, const Shape& strides);
+Shape scalar_output_strides(const Shape& shape, const Shape& strides);
+void binary_plan(const Shape& lshape, const Shape& lstrides, const Shape& rshape, const Shape& rstrides,
+                 Shape* shape, Shape* strides);
+
+// ---- engine (engine.cpp) -------------------------------------------------------------------------
+bool grad_enabled();
+void set_grad_enabled(bool on);
+trs_stream stream_for(int device);
+void check_cuda(int32_t status, const char* what);
+
+TensorP from_host(const float* data, const Shape& shape, int device);
+TensorP full(const Shape& shape, float value, int device);
+void to_host(const Tensor& t, float* out);                 // logical row-major order
+float item(const Tensor& t);
+void materialize(const std::shared_ptr<Storage>& st);
+void sync(int device);
+
+TensorP permute(const TensorP& t, const std::vector<i64>& dims, int node_kind);
+TensorP transpose(const TensorP& t, i64 d0, i64 d1);
+TensorP matrix_transpose(const TensorP& t);
+TensorP reverse_dims(const TensorP& t);
+TensorP select0(const TensorP& t, i64 index);
+TensorP detach(const TensorP& t);
+TensorP contiguous(const TensorP& t);
+
+TensorP unary(const TensorP& t, int op);                   // relu, exp, neg, sin, sqrt, reciprocal
+TensorP scalar_op(const TensorP& t, int op, float s, bool reflected);
+TensorP binary(const TensorP& l, const TensorP& r, int op);
+TensorP matmul(const TensorP& l, const TensorP& r);
+TensorP sum(const TensorP& t);
+
+TensorP set_requires_grad(const TensorP& t, bool on);
+void backward(const TensorP& root);
+TensorP grad_of(const TensorP& t);
+
+// Internal helpers shared with autograd.cpp
+TensorP make_tensor(View v);
+TensorP pointwise_node(int op, float imm, std::vector<View> args, const Shape& shape, const Shape& strides, int device);
+TensorP zeros_like_shape(const Shape& shape, int device);
+extern std::recursive_mutex g_engine_mu;
+
+}  // namespace trsh

@@ -1,0 +1,109 @@
+"""CPU-side checks of the host engine library: exports, layout planner vs the checker, error strings."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from torch_rs import _host
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "trs_host.h")
+
+
+def test_host_library_exports_every_declared_symbol():
+    text = open(HEADER).read()
+    names = sorted(set(re.findall(r"^(?:int32_t|const char\*)\s+(trsh_[a-z0-9_]+)\s*\(", text, flags=re.M)))
+    lib = ctypes.CDLL(_host.LIB_PATH)
+    assert len(names) >= 30
+    for name in names:
+        assert hasattr(lib, name), name
+    assert sorted(_host.EXPORTS) == names
+
+
+def test_cuda_tensor_creation_fails_loudly_without_a_device():
+    import torch_rs as torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(RuntimeError, match="no CUDA device"):
+        torch.tensor([1.0, 2.0], device="cuda")
+    with pytest.raises(RuntimeError, match="never falls back to the CPU"):
+        torch.tensor([1.0], device="cpu")
+    with pytest.raises(RuntimeError, match="pass device='cuda'"):
+        torch.zeros(3)
+
+
+def _arr(values):
+    return (ctypes.c_int64 * max(len(values), 1))(*values)
+
+
+def _random_view(rng):
+    """A random dense-or-sliced view: permuted contiguous base, optional singleton and step-2 axes."""
+    rank = int(rng.integers(0, 5))
+    base = [int(rng.choice([1, 2, 3, 4, 5])) for _ in range(rank)]
+    strides, s = [0] * rank, 1
+    for axis in range(rank - 1, -1, -1):
+        step = int(rng.choice([1, 1, 1, 2]))
+        strides[axis] = s * step
+        s *= base[axis] * step
+    perm = list(rng.permutation(rank)) if rank else []
+    return [base[p] for p in perm], [strides[p] for p in perm]
+
+
+def test_layout_planner_matches_the_checker_on_random_views():
+    import numpy as np
+    from oracle import ref
+    lib = _host.lib()
+    rng = np.random.default_rng(123)
+    checked = 0
+    for _ in range(3000):
+        shape, strides = _random_view(rng)
+        out = _arr([0] * len(shape))
+        assert lib.trsh_plan_unary(len(shape), _arr(shape), _arr(strides), out) == 0
+        assert list(out)[:len(shape)] == ref.unary_strides(shape, strides)
+        assert lib.trsh_plan_scalar(len(shape), _arr(shape), _arr(strides), out) == 0
+        assert list(out)[:len(shape)] == ref.scalar_strides(shape, strides)
+        other_shape, other_strides = _random_view(rng)
+        if rng.random() < 0.5:           # same-shape partner with another layout
+            other_shape = list(shape)
+            order = list(rng.permutation(len(shape)))
+            other_strides, s = [0] * len(shape), 1
+            for axis in order:
+                other_strides[axis] = s
+                s *= max(shape[axis], 1)
+        rank = ctypes.c_int32()
+        oshape, ostrides = _arr([0] * 8), _arr([0] * 8)
+        status = lib.trsh_plan_binary(len(shape), _arr(shape), _arr(strides), len(other_shape), _arr(other_shape),
+                                      _arr(other_strides), ctypes.byref(rank), oshape, ostrides)
+        try:
+            want_shape, want_strides = ref.binary_plan(shape, strides, other_shape, other_strides)
+        except ref.RefError as err:
+            assert err.kind == "ShapeMismatch" and status == 1
+            continue
+        assert status == 0
+        assert list(oshape)[:rank.value] == want_shape and list(ostrides)[:rank.value] == want_strides
+        checked += 1
+    assert checked > 500
+
+
+def test_layout_planner_reference_goldens():
+    import json
+    lib = _host.lib()
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))["strides"]
+    g = gold["singleton_channels_last"]
+    out = _arr([0] * 4)
+    assert lib.trsh_plan_unary(4, _arr(g["view_shape"]), _arr(g["view_strides"]), out) == 0
+    assert list(out) == g["expected"]
+    for case in gold["empty_scalar_op"]["cases"]:
+        n = len(case["shape"])
+        strides, s = [0] * n, 1
+        for axis in range(n - 1, -1, -1):
+            strides[axis] = s
+            s *= max(case["shape"][axis], 1)
+        out = _arr([0] * n)
+        assert lib.trsh_plan_scalar(n, _arr(case["shape"]), _arr(strides), out) == 0
+        assert list(out)[:n] == case["expected"]
+    rank = ctypes.c_int32()
+    oshape, ostrides = _arr([0] * 8), _arr([0] * 8)
+    status = lib.trsh_plan_binary(1, _arr([0]), _arr([1]), 1, _arr([2]), _arr([1]), ctypes.byref(rank), oshape, ostrides)
+    assert status == 1
+    assert b"The size of tensor a (0) must match the size of tensor b (2) at non-singleton dimension 0" in lib.trsh_last_error()

@@ -1,0 +1,264 @@
+"""GPU parity through the `torch_rs` surface (Python -> C++ host engine -> C ABI kernels) against the
+CPU checker: values, and the layout metadata (.shape/.stride()/.storage_offset()) of every result, the
+way the reference's differential tests compare them (tests/test_operation_chains_reference.py:213-228)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import torch_rs as torch
+from oracle import ref
+from oracle.ref import RefTensor
+from torch_rs._device import launch_count
+
+pytestmark = pytest.mark.gpu
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+DEV = "cuda:0"
+
+
+def hexf(items):
+    return np.array([int(h, 16) for h in items], dtype=np.uint32).view(np.float32)
+
+
+def bits(a):
+    return [f"{b:08x}" for b in np.ascontiguousarray(a, dtype=np.float32).reshape(-1).view(np.uint32)]
+
+
+def rnd(seed, *shape, scale=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * scale).astype(np.float32)
+
+
+def check_same(t, r: RefTensor, exact=True, ulp=0):
+    assert list(t.shape) == r.shape
+    assert list(t.stride()) == r.strides, (t.stride(), r.strides)
+    assert t.storage_offset() == r.offset
+    got, want = t.numpy(), r.logical()
+    if exact:
+        assert ref.same_bits_or_nan(got, want).all()
+    else:
+        assert ref.ulp_distance(got, want).max() <= ulp
+
+
+def test_relu_add_contiguous_is_one_kernel():
+    x, y = np.random.default_rng(0).uniform(-1, 1, (300, 257)).astype(np.float32), np.random.default_rng(1).uniform(-1, 1, (300, 257)).astype(np.float32)
+    tx, ty = torch.tensor(x, device=DEV), torch.tensor(y, device=DEV)
+    before = launch_count()
+    out = torch.relu(tx + ty)
+    assert out.is_pending()
+    out.materialize()
+    assert launch_count() - before == 1
+    assert not out.is_pending()
+    check_same(out, (RefTensor.from_numpy(x) + RefTensor.from_numpy(y)).relu())
+    assert not out.shares_storage_with(tx)
+
+
+def test_transposed_broadcast_exp_chain_metadata_and_values():
+    n, m = 160, 96
+    xs, b = rnd(0, n, m), (0.1 * rnd(1, n)).astype(np.float32)
+    x, bt = torch.tensor(xs, device=DEV), torch.tensor(b, device=DEV)
+    before = launch_count()
+    out = torch.exp(2.0 * torch.relu(x.mT + bt)) - x.mT
+    assert out.stride() == x.mT.stride()          # the chain stays in x's physical order
+    out.materialize()
+    assert launch_count() - before == 1           # five ops, one kernel
+    rx = RefTensor.from_numpy(xs)
+    expected = (2.0 * (rx.mT + RefTensor.from_numpy(b)).relu()).exp() - rx.mT
+    check_same(out, expected, exact=False, ulp=2)
+
+
+def test_every_intermediate_matches_when_held():
+    xs = rnd(2, 64, 48)
+    x = torch.tensor(xs, device=DEV)
+    rx = RefTensor.from_numpy(xs)
+    a = x.mT + 1.5
+    b = a.relu()
+    c = b * x.mT
+    d = c - 0.25
+    before = launch_count()
+    d.materialize()
+    assert launch_count() - before == 1           # held intermediates become extra outputs of the same kernel
+    ra = rx.mT + 1.5
+    rb = ra.relu()
+    rc = rb * rx.mT
+    rd = rc - 0.25
+    for t, r in ((a, ra), (b, rb), (c, rc), (d, rd)):
+        check_same(t, r)
+
+
+def test_views_select_permute_T():
+    base = rnd(3, 2, 6, 5)
+    t = torch.tensor(base, device=DEV)
+    r = RefTensor.from_numpy(base)
+    v, rv = t.select(0, 1).T, r.select0(1).T
+    assert v.storage_offset() == rv.offset and list(v.stride()) == rv.strides
+    check_same(v.relu(), rv.relu())
+    p, rp = t.permute(2, 0, 1), r.permute([2, 0, 1])
+    row = rnd(4, 6)
+    check_same(p * torch.tensor(row, device=DEV), rp * RefTensor.from_numpy(row))
+    check_same(t[1] + t[0], r.select0(1) + r.select0(0))
+    assert np.array_equal(torch.transpose(t, 0, 2).numpy(), base.transpose(2, 1, 0))
+
+
+def test_layouts_disagree_uses_tiled_kernel_and_matches():
+    a, b = rnd(5, 200, 120), rnd(6, 120, 200)
+    out = torch.tensor(a, device=DEV).mT + torch.tensor(b, device=DEV)
+    check_same(out, RefTensor.from_numpy(a).mT + RefTensor.from_numpy(b))
+
+
+def test_broadcast_golden_and_errors():
+    g = GOLD["broadcast_arithmetic"]
+    left = torch.tensor(np.array(g["left"]["values"], dtype=np.float32).reshape(g["left"]["shape"]), device=DEV)
+    right = torch.tensor(np.array(g["right"]["values"], dtype=np.float32).reshape(g["right"]["shape"]), device=DEV)
+    assert (left + right).numpy().reshape(-1).tolist() == g["add"]
+    assert (left - right).numpy().reshape(-1).tolist() == g["sub"]
+    assert torch.multiply(left, right).numpy().reshape(-1).tolist() == g["mul"]
+    assert (left / right).numpy().reshape(-1).tolist() == g["div"]
+    with pytest.raises(RuntimeError, match=r"The size of tensor a \(0\) must match the size of tensor b \(2\) at non-singleton dimension 0"):
+        torch.zeros(0, device=DEV) + torch.ones(2, device=DEV)
+    empty = torch.zeros(2, 0, 3, device=DEV) + torch.ones(1, 1, 3, device=DEV)
+    assert empty.shape == (2, 0, 3) and empty.numpy().size == 0
+
+
+def test_matmul_goldens_errors_and_precision():
+    assert torch.get_float32_matmul_precision() == "highest"
+    a = torch.tensor(np.arange(1, 7, dtype=np.float32).reshape(2, 3), device=DEV)
+    b = torch.tensor(np.arange(7, 13, dtype=np.float32).reshape(3, 2), device=DEV)
+    out = torch.matmul(a, b)
+    assert out.shape == (2, 2) and out.stride() == (2, 1)
+    assert out.numpy().reshape(-1).tolist() == [58.0, 64.0, 139.0, 154.0]
+    assert (a.T @ b.T).shape == (3, 3)
+    with pytest.raises(RuntimeError, match=r"mat1 and mat2 shapes cannot be multiplied \(2x3 and 4x2\)"):
+        torch.zeros(2, 3, device=DEV) @ torch.zeros(4, 2, device=DEV)
+    with pytest.raises(RuntimeError, match="matmul currently requires two rank-2 tensors"):
+        torch.zeros(3, device=DEV) @ torch.zeros(3, 2, device=DEV)
+    assert not out.requires_grad
+
+
+def test_batched_bias_relu_fuses_into_the_matmul():
+    batch, m, n, k = 4, 96, 128, 64
+    xs, ws = rnd(7, batch, m, k), rnd(8, batch, n, k, scale=1 / 8)
+    bias = np.random.default_rng(9).uniform(-0.1, 0.1, n).astype(np.float32)
+    x, w, bt = torch.tensor(xs, device=DEV), torch.tensor(ws, device=DEV), torch.tensor(bias, device=DEV)
+    before = launch_count()
+    out = torch.relu(x @ w.mT + bt).materialize()
+    launches = launch_count() - before
+    assert launches <= 3           # GEMM with the bias+relu epilogue (plus operand preparation for the tensor-core path)
+    rx, rw = RefTensor.from_numpy(xs), RefTensor.from_numpy(ws)
+    got = out.numpy()
+    for i in range(batch):
+        want = (rx.select0(i).matmul(rw.select0(i).mT) + RefTensor(bias, [n])).relu().logical().astype(np.float64)
+        rms = np.sqrt(np.mean(want ** 2))
+        assert np.all(np.abs(got[i] - want) <= 1e-5 * np.sqrt(k) * np.maximum(np.abs(want), rms) + 1e-30)
+
+
+def test_autograd_goldens():
+    a = GOLD["autograd"]
+    x = torch.tensor(a["square_sum"]["x"], device=DEV, requires_grad=True)
+    (x * x).sum().backward()
+    assert x.grad.tolist() == a["square_sum"]["grad_first"]
+    (x * x).sum().backward()
+    assert x.grad.tolist() == a["square_sum"]["grad_second"]
+
+    u = a["unbroadcast_both"]
+    left = torch.tensor(np.array(u["left"]["values"], dtype=np.float32).reshape(u["left"]["shape"]), device=DEV, requires_grad=True)
+    right = torch.tensor(np.array(u["right"]["values"], dtype=np.float32).reshape(u["right"]["shape"]), device=DEV, requires_grad=True)
+    (left * right).sum().backward()
+    assert left.grad.numpy().reshape(-1).tolist() == u["left_grad"]
+    assert right.grad.numpy().reshape(-1).tolist() == u["right_grad"]
+
+    r = a["rank_zero_view"]
+    for scalar_on_left in (True, False):
+        source = torch.tensor(np.array(r["source_values"], dtype=np.float32).reshape(r["source_shape"]), device=DEV, requires_grad=True)
+        view = source[1].transpose(0, 1)
+        scalar = torch.tensor(r["scalar"], device=DEV, requires_grad=True)
+        out = scalar * view if scalar_on_left else view * scalar
+        assert out.shape == (3, 2) and out.stride() == (1, 3)
+        out.sum().backward()
+        assert scalar.grad.numpy().reshape(-1).tolist() == r["scalar_grad"]
+        assert source.grad.numpy().reshape(-1).tolist() == r["source_grad"]
+
+    z = a["negative_zero_first"]
+    left = torch.tensor([2.0], device=DEV, requires_grad=True)
+    (left * torch.tensor([-0.0], device=DEV)).sum().backward()
+    assert bits(left.grad.numpy()) == [z["same_count_bits"]]
+    bl = torch.tensor(2.0, device=DEV, requires_grad=True)
+    (bl * torch.tensor([-0.0, -0.0], device=DEV)).sum().backward()
+    assert bits(bl.grad.numpy()) == [z["broadcast_bits"]]
+
+
+def test_relu_vjp_golden_bits_and_graph_is_freed():
+    g = GOLD["relu_vjp_bits"]
+    leaf = torch.tensor(hexf(g["input"]), device=DEV, requires_grad=True)
+    weights = torch.tensor(hexf(g["weights"]), device=DEV)
+    out = torch.nn.functional.relu(leaf)
+    assert out.requires_grad and not out.is_leaf and out._grad_fn_name() == "ReluBackward0"
+    loss = (out * weights).sum()
+    torch.autograd.backward(loss)
+    assert bits(leaf.grad.numpy()) == g["expected_gradient"]
+    with pytest.raises(RuntimeError, match="Trying to backward through the graph a second time"):
+        loss.backward()
+    with pytest.raises(RuntimeError, match="does not require grad"):
+        weights.sum().backward()
+    with torch.no_grad():
+        assert not torch.relu(leaf).requires_grad
+
+
+def test_exp_sub_add_backward_edges_exist_on_cuda():
+    xs = rnd(10, 33, 17)
+    x = torch.tensor(xs, device=DEV, requires_grad=True)
+    y = torch.tensor(rnd(11, 17), device=DEV, requires_grad=True)
+    loss = (torch.exp(x * 0.5) - (x + y)).sum()
+    loss.backward()
+    want_x = 0.5 * np.exp(0.5 * xs.astype(np.float64)) - 1.0
+    assert np.allclose(x.grad.numpy(), want_x, rtol=2e-6, atol=1e-6)
+    assert np.allclose(y.grad.numpy(), -33.0 * np.ones(17), rtol=1e-6)
+
+
+def test_mlp_forward_backward_matches_composed_reference():
+    # loss = (relu(X @ W1 + b1) @ W2).sum(): the reference primitives composed (matmul, add, relu, sum and
+    # the VJPs of src/tensor.rs:3002-3107, 4422-4432) define the expected gradients.
+    bsz, d, h, o = 256, 128, 192, 64
+    xs, w1s, w2s = rnd(12, bsz, d), rnd(13, d, h, scale=1 / 8), rnd(14, h, o, scale=1 / 8)
+    b1s = (0.1 * rnd(15, h)).astype(np.float32)
+    X = torch.tensor(xs, device=DEV)
+    W1, W2 = torch.tensor(w1s, device=DEV, requires_grad=True), torch.tensor(w2s, device=DEV, requires_grad=True)
+    b1 = torch.tensor(b1s, device=DEV, requires_grad=True)
+    loss = (torch.relu(X @ W1 + b1) @ W2).sum()
+    loss.backward()
+    rX, rW1, rW2 = RefTensor.from_numpy(xs), RefTensor.from_numpy(w1s), RefTensor.from_numpy(w2s)
+    Z = rX.matmul(rW1) + RefTensor(b1s, [h])
+    H = Z.relu()
+    Y = H.matmul(rW2)
+    dY = RefTensor.from_numpy(np.ones((bsz, o), dtype=np.float32))
+    dW2 = H.T.matmul(dY).logical()
+    dH = dY.matmul(rW2.T)
+    dZ = RefTensor.from_numpy(Z.relu_vjp(dH.logical()))
+    db1 = ref.unbroadcast(dZ.logical(), [bsz, h], [h])
+    dW1 = rX.T.matmul(dZ).logical()
+
+    def close(got, want, k):
+        want = want.astype(np.float64)
+        rms = np.sqrt(np.mean(want ** 2))
+        return np.all(np.abs(got - want) <= 1e-5 * np.sqrt(k) * np.maximum(np.abs(want), rms) + 1e-30)
+
+    assert close(W2.grad.numpy(), dW2, bsz)
+    assert close(W1.grad.numpy(), dW1, bsz)
+    assert close(b1.grad.numpy(), db1, bsz)
+    assert abs(loss.item() - Y.sum()) <= 1e-5 * np.sqrt(bsz * o) * float(np.abs(Y.logical()).sum()) / (bsz * o) * 100
+    assert W1.grad.is_contiguous() and W1.grad.shape == (d, h)
+
+
+def test_item_tolist_and_scalar_forms():
+    xs = rnd(16, 5, 3)
+    x = torch.tensor(xs, device=DEV)
+    rx = RefTensor.from_numpy(xs)
+    check_same(1.5 - x, 1.5 - rx)
+    check_same(2.0 / x.T, 2.0 / rx.T)
+    check_same(x / 3.0, rx / 3.0)
+    check_same(-x, rx.neg())
+    assert x.sum().item() == pytest.approx(float(xs.sum()), rel=1e-5)
+    with pytest.raises(RuntimeError, match="item requires one element, got 15"):
+        x.item()
+    with pytest.raises(IndexError, match="index 7 is out of bounds for dimension 0 with size 5"):
+        x[7]
