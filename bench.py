@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the fused pointwise hot path (and, as extra figures, f32 matmul) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this build (one rank per GPU under torchrun)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU algorithm on the host cores
+
+Workload (N=1): `exp(2.0 * relu(x.mT + b)) - x.mT`, x f32 [8192,8192] ~N(0,1) read through a
+transposed view, b f32 [8192] ~N(0,0.1) broadcast, scalar 2.0 — a five-op chain run as ONE kernel.
+A step builds the chain through the public `torch_rs` surface and forces its execution.
+With N ranks every rank runs the same-sized shard of an N-times larger batch (weak scaling, no
+data-path collective).  Prints ONE JSON line (rank 0).
+
+Algorithmic bytes per step and GPU: 8 B per element (x read once, result written once) + b
+= 8*8192*8192 + 4*8192 = 536,903,680 B.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "pytorch-rs_b200"))
+sys.path.insert(0, ROOT)
+
+N_SIDE = 8192
+ALGO_BYTES = 8 * N_SIDE * N_SIDE + 4 * N_SIDE
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        peaks = json.load(open(path))
+        return float(peaks["hbm_gbs"]), "measured", peaks
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback", {}
+
+
+def make_inputs(seed, rows=N_SIDE):
+    """Seeded synthetic inputs with the workload's shapes and distributions (NumPy default_rng)."""
+    rng = np.random.default_rng(seed)
+    xs = rng.standard_normal((rows, N_SIDE)).astype(np.float32)      # storage of x; the operand is xs.mT
+    b = (0.1 * rng.standard_normal(rows)).astype(np.float32)
+    return xs, b
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        clocks, reasons, max_clock = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if clocks:
+            # under load = the upper half of the samples (the sampler also sees idle gaps)
+            clocks.sort()
+            out.update(sm_mhz=statistics.median(clocks[len(clocks) // 2:]), sm_max_mhz=max_clock,
+                       reasons=sorted(reasons), samples=len(clocks))
+        return out
+
+
+def cpu_chain(xs, b):
+    """The same chain through the CPU checker, op by op as the reference engine runs it."""
+    from oracle.ref import RefTensor
+    x, bt = RefTensor.from_numpy(xs), RefTensor.from_numpy(b)
+    return (2.0 * (x.mT + bt).relu()).exp() - x.mT
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's CPU algorithm for this chain (C++ restatement in oracle/, since
+    no Rust toolchain exists to build the original) on the host cores; single-threaded, as the
+    reference engine is."""
+    if rank != 0:
+        return
+    from oracle import ref
+    ref.build()
+    total_steps = args.steps + args.warmup
+    rows = N_SIDE if total_steps * 5.0 <= 150 else 2048
+    xs, b = make_inputs(0, rows)
+    bytes_per_step = 8 * rows * N_SIDE + 4 * rows
+    for _ in range(args.warmup):
+        cpu_chain(xs, b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_chain(xs, b)
+    dt = time.perf_counter() - t0
+    value = bytes_per_step * args.steps / dt / 1e9
+    sample = f"{rows} of {N_SIDE} physical rows of x per step ({bytes_per_step} algorithmic bytes)"
+    line = {
+        "impl": "reference", "metric": "fused pointwise GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "exp(2.0*relu(x.mT+b))-x.mT, x f32 [8192,8192] via transposed view, b [8192] broadcast",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample,
+                         "host_cores": os.cpu_count()},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_region(stream, fn, steps):
+    from torch_rs._device import Event
+    e0, e1 = Event(), Event()
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    e1.sync()
+    return e0.elapsed_ms(e1)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch_rs as torch
+    from torch_rs import _abi, _host
+    from torch_rs._device import Stream, launch_count
+    import ctypes
+
+    dist = None
+    if world > 1:
+        import torch as pt                      # plumbing only: rendezvous, barrier, max over ranks
+        import torch.distributed as dist
+        pt.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=pt.device("cuda", local_rank))
+
+    def barrier():
+        torch.synchronize(local_rank)
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(value):
+        if dist is None:
+            return value
+        import torch as pt
+        t = pt.tensor([value], dtype=pt.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev = f"cuda:{local_rank}"
+    raw = ctypes.c_void_p()
+    _host.check(_host.lib().trsh_stream(local_rank, ctypes.byref(raw)))
+    stream = Stream.__new__(Stream)
+    stream.device, stream.handle = local_rank, raw           # the engine's own stream: events go where the kernels go
+
+    xs, b = make_inputs(rank)
+    x, bt = torch.tensor(xs, device=dev), torch.tensor(b, device=dev)
+    held = [None]
+
+    def step():
+        held[0] = (torch.exp(2.0 * torch.relu(x.mT + bt)) - x.mT).materialize()
+
+    # ---- device-resident throughput ---------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    launches0 = launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ms = time_region(stream, step, args.steps)
+        barrier()
+    launches = launch_count() - launches0
+    ms = max_over_ranks(ms)
+    ms_per_step = ms / args.steps
+    value = world * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+    clock_info = clocks.summary()
+
+    # ---- parity spot check on this rank's result (checker on a slab of physical rows) ---------
+    parity = None
+    if rank == 0:
+        from oracle import ref
+        rows = 64
+        got = held[0].mT.numpy()[:rows]                        # physical rows of the result
+        want = cpu_chain(xs[:rows], b[:rows]).mT.logical()
+        parity = {"max_ulp_vs_cpu": int(ref.ulp_distance(got, want).max()), "rows_checked": rows, "tolerance_ulp": 2}
+
+    # ---- end to end: pinned host buffers in, result read back, every step -----------------------
+    x_host, b_host = torch.pinned_empty(N_SIDE, N_SIDE), torch.pinned_empty(N_SIDE)
+    out_host = torch.pinned_empty(N_SIDE, N_SIDE)
+    x_host[...] = xs
+    b_host[...] = b
+
+    def step_e2e():
+        xd, bd = torch.tensor(x_host, device=dev), torch.tensor(b_host, device=dev)
+        out = torch.exp(2.0 * torch.relu(xd.mT + bd)) - xd.mT
+        out.mT.copy_to_host(out_host)          # the result's storage order; waits for the device
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    torch.synchronize(local_rank)
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
+    e2e_value = world * ALGO_BYTES / (e2e_ms * 1e-3) / 1e9
+    if rank == 0:
+        assert np.array_equal(out_host[:8].view(np.uint32), held[0].mT.numpy()[:8].view(np.uint32))
+
+    # ---- extra figures: contiguous relu(x+y) and f32 matmul 4096^3 (per GPU, rank 0) --------------
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        n1 = 4096
+        rng = np.random.default_rng(0)
+        sets = [(torch.tensor(rng.uniform(-1, 1, (n1, n1)).astype(np.float32), device=dev),
+                 torch.tensor(rng.uniform(-1, 1, (n1, n1)).astype(np.float32), device=dev)) for _ in range(4)]
+        it = [0]
+
+        def c1():
+            xa, ya = sets[it[0] % 4]
+            it[0] += 1
+            held[0] = torch.relu(xa + ya).materialize()
+        for _ in range(5):
+            c1()
+        torch.synchronize(local_rank)
+        c1_ms = time_region(stream, c1, 40) / 40
+        extra["relu_add_4096"] = {"GB/s": 12 * n1 * n1 / (c1_ms * 1e-3) / 1e9, "ms": c1_ms,
+                                  "note": "4 rotating operand sets (768 MiB) defeat L2"}
+        a = torch.tensor((rng.standard_normal((n1, n1)) / 64).astype(np.float32), device=dev)
+        bm = torch.tensor((rng.standard_normal((n1, n1)) / 64).astype(np.float32), device=dev)
+        del sets
+
+        def c3():
+            held[0] = torch.matmul(a, bm).materialize()
+        for _ in range(3):
+            c3()
+        torch.synchronize(local_rank)
+        c3_ms = time_region(stream, c3, 10) / 10
+        desc = _abi.GemmDesc()
+        desc.batch, desc.m, desc.n, desc.k = 1, n1, n1, n1
+        desc.a, desc.b, desc.c = a.data_ptr(), bm.data_ptr(), held[0].data_ptr()
+        desc.a_row_stride, desc.a_col_stride, desc.b_row_stride, desc.b_col_stride, desc.c_row_stride = n1, 1, n1, 1, n1
+        algo = ctypes.c_int32()
+        _abi.lib().trs_matmul_select_algo(ctypes.byref(desc), ctypes.byref(algo))
+        extra["matmul_4096"] = {"TFLOP/s": 2 * n1 ** 3 / (c3_ms * 1e-3) / 1e12, "ms": c3_ms,
+                                "algo": {1: "simt_fp32", 2: "tcgen05_3xtf32"}.get(algo.value, str(algo.value))}
+
+    # ---- CPU baseline (rank 0, N=1): the whole workload through the checker, single thread ---------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        times = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            cpu_chain(xs, b)
+            times.append(time.perf_counter() - t0)
+        cpu_baseline = {"value": ALGO_BYTES / statistics.median(times) / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                        "sample": "the full workload, median of 3 runs", "host_cores": os.cpu_count()}
+
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    peak, peak_kind, _ = measured_peaks()
+    achieved = ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+    traffic = None
+    try:
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))["pointwise_c2_dram_bytes_per_launch"]
+    except Exception:
+        pass
+    line = {
+        "metric": "fused pointwise GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "exp(2.0*relu(x.mT+b))-x.mT, x f32 [8192,8192] via transposed view, b [8192] broadcast, "
+                               "one fused kernel per step, per GPU",
+                   "l2": "inputs+outputs 512 MiB per step, larger than the 126 MB L2", "parallelism": f"dp{world}",
+                   "algorithmic_bytes_per_step_per_gpu": ALGO_BYTES},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_source": f"of {peak_kind}", "kernel": "trs_pw (vector class)"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ALGO_BYTES // 2 + 2 * N_SIDE,
+                "d2h_bytes_per_step": 4 * N_SIDE * N_SIDE, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": launches, "clocks": clock_info, "parity": parity, "extra": extra,
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the relu(x+y) and matmul side figures")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,9 @@ const char* trsh_last_error(void) { return t_error.c_str(); }
 int32_t trsh_from_host(const float* data, int32_t rank, const int64_t* shape, int32_t device, trsh_tensor* out) {
     return guarded([&] { *out = wrap(from_host(data, shape_of(rank, shape), device)); });
 }
+int32_t trsh_from_pinned_host(const float* data, int32_t rank, const int64_t* shape, int32_t device, trsh_tensor* out) {
+    return guarded([&] { *out = wrap(from_host(data, shape_of(rank, shape), device, true)); });
+}
 int32_t trsh_full(int32_t rank, const int64_t* shape, float value, int32_t device, trsh_tensor* out) {
     return guarded([&] { *out = wrap(full(shape_of(rank, shape), value, device)); });
 }

@@ -66,14 +66,16 @@ TensorP make_tensor(View v) {
     return t;
 }
 
-TensorP from_host(const float* data, const Shape& shape, int device) {
+TensorP from_host(const float* data, const Shape& shape, int device, bool pinned) {
     for (i64 d : shape) if (d < 0) throw Error(ErrKind::InvalidArgument, "negative dimension");
     const i64 n = element_count(shape);
     auto st = alloc_storage(n, device);
     if (n > 0) {
         trs_stream s = stream_for(device);
         check_cuda(trs_memcpy_h2d(st->ptr, data, (size_t)n * sizeof(float), s), "host to device copy");
-        check_cuda(trs_stream_sync(s), "host to device copy");   // the source is pageable caller memory
+        // A pageable source may be released by the caller at once; a pinned source is promised to
+        // stay untouched until the stream reaches the copy, so the call returns without waiting.
+        if (!pinned) check_cuda(trs_stream_sync(s), "host to device copy");
     }
     return make_tensor(View{st, shape, contiguous_strides(shape), 0});
 }

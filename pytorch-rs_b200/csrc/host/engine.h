@@ -117,7 +117,7 @@ void set_grad_enabled(bool on);
 trs_stream stream_for(int device);
 void check_cuda(int32_t status, const char* what);
 
-TensorP from_host(const float* data, const Shape& shape, int device);
+TensorP from_host(const float* data, const Shape& shape, int device, bool pinned = false);
 TensorP full(const Shape& shape, float value, int device);
 void to_host(const Tensor& t, float* out);                 // logical row-major order
 float item(const Tensor& t);

@@ -27,9 +27,27 @@ def tensor(data, *, dtype=None, device=None, requires_grad=False) -> Tensor:
     array = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
     shape = (ctypes.c_int64 * max(array.ndim, 1))(*array.shape)
     out = ctypes.c_void_p()
-    _host.check(_host.lib().trsh_from_host(array.ctypes.data, array.ndim, shape, index, ctypes.byref(out)))
+    # Arrays that live in page-locked staging memory (torch_rs.pinned_empty) are copied without waiting.
+    copy = _host.lib().trsh_from_pinned_host if _device.is_pinned(array) else _host.lib().trsh_from_host
+    _host.check(copy(array.ctypes.data, array.ndim, shape, index, ctypes.byref(out)))
     t = _wrap(out)
     return t.requires_grad_(True) if requires_grad else t
+
+
+def pinned_empty(*size) -> np.ndarray:
+    """A float32 NumPy array in page-locked host memory, for overlapping host<->device copies."""
+    size = _sizes(size)
+    buf = _device.PinnedBuffer(int(np.prod(size)) if size else 1)
+    _pinned_keep[buf.ptr] = buf          # stays page-locked until pinned_free(array)
+    return buf.array.reshape(size)
+
+
+def pinned_free(array) -> None:
+    """Release a staging array from pinned_empty (no copy may still be in flight)."""
+    _pinned_keep.pop(array.ctypes.data, None)
+
+
+_pinned_keep = {}
 
 
 def full(size, fill_value, *, dtype=None, device=None, requires_grad=False) -> Tensor:

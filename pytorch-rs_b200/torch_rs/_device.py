@@ -117,6 +117,16 @@ class DeviceBuffer:
         return out
 
 
+_pinned_ranges = {}     # start address -> (end address, owner) of live page-locked buffers
+
+
+def is_pinned(array) -> bool:
+    """Whether a NumPy array's bytes lie entirely inside a live PinnedBuffer."""
+    start = array.ctypes.data
+    end = start + array.nbytes
+    return any(lo <= start and end <= hi for lo, (hi, _) in _pinned_ranges.items())
+
+
 class PinnedBuffer:
     """Page-locked host staging memory exposed as a NumPy array (for timed host<->device copies)."""
 
@@ -126,10 +136,12 @@ class PinnedBuffer:
         _abi.check(_abi.lib().trs_malloc_host(max(self.count, 1) * 4, ctypes.byref(ptr)))
         self.ptr = ptr.value
         self.array = np.ctypeslib.as_array(ctypes.cast(self.ptr, ctypes.POINTER(ctypes.c_float)), shape=(self.count,))
+        _pinned_ranges[self.ptr] = (self.ptr + max(self.count, 1) * 4, None)
 
     def __del__(self):
         ptr, self.ptr = getattr(self, "ptr", None), None
         if ptr:
+            _pinned_ranges.pop(ptr, None)
             try:
                 _abi.lib().trs_free_host(ptr)
             except Exception:

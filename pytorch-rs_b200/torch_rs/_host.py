@@ -18,6 +18,7 @@ F32P = ctypes.POINTER(ctypes.c_float)
 
 _PROTOTYPES = {
     "trsh_from_host": [ctypes.c_void_p, ctypes.c_int32, I64P, ctypes.c_int32, HP],
+    "trsh_from_pinned_host": [ctypes.c_void_p, ctypes.c_int32, I64P, ctypes.c_int32, HP],
     "trsh_full": [ctypes.c_int32, I64P, ctypes.c_float, ctypes.c_int32, HP],
     "trsh_to_host": [H, ctypes.c_void_p],
     "trsh_item": [H, F32P],

@@ -170,6 +170,13 @@ class Tensor:
         _host.check(_host.lib().trsh_to_host(self._h, out.ctypes.data))
         return out.reshape(shape)
 
+    def copy_to_host(self, out):
+        """Write the values in logical order into a caller-provided float32 array (e.g. pinned memory)."""
+        if out.dtype != np.float32 or not out.flags.c_contiguous or out.size != self.numel():
+            raise ValueError("copy_to_host needs a C-contiguous float32 array with numel elements")
+        _host.check(_host.lib().trsh_to_host(self._h, out.ctypes.data))
+        return out
+
     def cpu(self):
         """Values in logical order as a NumPy array (CPU tensors themselves belong to the reference engine)."""
         return self.numpy()
