@@ -19,9 +19,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import threading
 import time
 
@@ -54,59 +52,64 @@ def make_inputs(seed, rows=N_SIDE):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and clock-event reasons through NVML on a thread while the timed region (and
+    an untimed post-roll of the same steps, so that a millisecond-long region still gets samples) runs."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
+        self.samples = []
+        self.reasons = set()
+        self.max_clock = None
+        self.stop = threading.Event()
+        self.thread = None
+        self.nvml = None
+
+    def _physical_index(self):
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            parts = [p for p in visible.split(",") if p.strip()]
+            if self.gpu_index < len(parts) and parts[self.gpu_index].strip().isdigit():
+                return int(parts[self.gpu_index])
+        return self.gpu_index
+
+    def _run(self, handle):
+        nv = self.nvml
+        while not self.stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def __enter__(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_clock = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._run, args=(handle,), daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.thread = None
         return self
 
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except Exception:
-                self.proc.kill()
+        self.stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if not self.path or not os.path.exists(self.path):
-            return out
-        clocks, reasons, max_clock = [], set(), None
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.path)
-        if clocks:
-            # under load = the upper half of the samples (the sampler also sees idle gaps)
-            clocks.sort()
-            out.update(sm_mhz=statistics.median(clocks[len(clocks) // 2:]), sm_max_mhz=max_clock,
-                       reasons=sorted(reasons), samples=len(clocks))
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_clock, "reasons": sorted(self.reasons), "samples": len(self.samples),
+               "how": "NVML on a thread every ~2 ms over the timed region plus an untimed post-roll of the same steps"}
+        if self.samples:
+            ordered = sorted(self.samples)
+            out["sm_mhz"] = statistics.median(ordered[len(ordered) // 2:])      # upper half = under load
         return out
 
 
@@ -208,8 +211,13 @@ def run_ours(args, rank, world, local_rank):
     launches0 = launch_count()
     with ClockSampler(local_rank) as clocks:
         ms = time_region(stream, step, args.steps)
+        launches = launch_count() - launches0
         barrier()
-    launches = launch_count() - launches0
+        post_roll_until = time.perf_counter() + 0.4       # same steps, untimed, so the sampler sees load
+        while time.perf_counter() < post_roll_until:
+            for _ in range(20):
+                step()
+            torch.synchronize(local_rank)
     ms = max_over_ranks(ms)
     ms_per_step = ms / args.steps
     value = world * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9

@@ -3,8 +3,12 @@
 #include "common.h"
 
 namespace trs {
-int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream);
+// `gate`: optional device word; when non-NULL the kernel returns at once unless *gate != 0.
+int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate = nullptr);
 // Whether the tensor-core path can take this descriptor (alignment and size rules).
 bool gemm_tc_eligible(const trs_gemm_desc& g);
 int32_t gemm_tc_launch(const trs_gemm_desc& g, trs_stream stream);
+size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g);
+int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream stream);
+int32_t gemm_check_status(int device);
 }  // namespace trs

@@ -22,7 +22,8 @@ __device__ __forceinline__ float ref_relu_vjp(float x, float g) {
 }
 
 template <bool A_KFAST, bool B_NFAST>
-__global__ void __launch_bounds__(256) gemm_simt_kernel(const trs_gemm_desc g) {
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const trs_gemm_desc g, const unsigned int* __restrict__ gate) {
+    if (gate != nullptr && *gate == 0u) return;
     __shared__ __align__(16) float As[2][BK][BM + PAD];
     __shared__ __align__(16) float Bs[2][BK][BN + PAD];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -120,15 +121,15 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const trs_gemm_desc g) {
 
 }  // namespace
 
-int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream) {
+int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate) {
     dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
     if (grid.y > 65535 || grid.z > 65535) return fail(TRS_ERR_UNSUPPORTED, "matmul grid too large for the SIMT kernel");
     const bool a_kfast = g.a_col_stride == 1 || g.a_row_stride != 1;
     const bool b_nfast = g.b_col_stride == 1 || g.b_row_stride != 1;
-    if (a_kfast && b_nfast) gemm_simt_kernel<true, true><<<grid, 256, 0, stream->stream>>>(g);
-    else if (a_kfast) gemm_simt_kernel<true, false><<<grid, 256, 0, stream->stream>>>(g);
-    else if (b_nfast) gemm_simt_kernel<false, true><<<grid, 256, 0, stream->stream>>>(g);
-    else gemm_simt_kernel<false, false><<<grid, 256, 0, stream->stream>>>(g);
+    if (a_kfast && b_nfast) gemm_simt_kernel<true, true><<<grid, 256, 0, stream->stream>>>(g, gate);
+    else if (a_kfast) gemm_simt_kernel<true, false><<<grid, 256, 0, stream->stream>>>(g, gate);
+    else if (b_nfast) gemm_simt_kernel<false, true><<<grid, 256, 0, stream->stream>>>(g, gate);
+    else gemm_simt_kernel<false, false><<<grid, 256, 0, stream->stream>>>(g, gate);
     TRS_CUDA(cudaGetLastError());
     count_launch();
     return TRS_OK;

@@ -1,7 +1,479 @@
-// Placeholder translation unit for the tensor-core matmul (filled in by the tcgen05 kernel).
+// Tensor-core float32 matmul for sm_100a: TMA-fed tcgen05.mma kind::tf32 with the 3-product
+// error-compensated split ("3xTF32"), FP32 accumulation in tensor memory, fused epilogues.
+//
+// Replaces Tensor::matmul's loops (pytorch-rs src/tensor.rs:2453-2533, 3889-3966) for aligned
+// shapes while honouring float32 matmul precision "highest": each operand a is split into
+// hi = tf32(a) and lo = tf32(a - hi); the product uses hi*hi + hi*lo + lo*hi, dropping only the
+// lo*lo term (relative 2^-22), so the result stays within the path's rel 1e-5*sqrt(K) tolerance.
+//
+// Two kernels:
+//   split_tf32_kernel  reads an operand through its (arbitrary) strides once and writes the hi
+//                      and lo planes K-major ([rows, K_pad], K_pad a multiple of 32, zero padded)
+//                      into scratch memory.  Transposed views (.mT operands, the backward GEMMs)
+//                      are handled here, so the GEMM itself sees one layout only.
+//   gemm_tf32x3_kernel one 128x256 output tile per CTA.  Warp 0 drives TMA (no multicast) into a
+//                      2-stage ring of {A_hi, A_lo, B_hi, B_lo} 128-byte-swizzled tiles, warp 1
+//                      issues 12 tcgen05.mma per stage into a 128x256 FP32 accumulator in TMEM,
+//                      warps 2-5 read it back with tcgen05.ld and apply the epilogue.
+// Every wait on an mbarrier is bounded; on a timeout the kernel records an error word, releases
+// its tensor memory and returns, and the host reports TRS_ERR_DEVICE_STATUS.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.h"
 #include "gemm.h"
 
 namespace trs {
-bool gemm_tc_eligible(const trs_gemm_desc&) { return false; }
-int32_t gemm_tc_launch(const trs_gemm_desc&, trs_stream) { return fail(TRS_ERR_UNSUPPORTED, "tensor-core matmul not built"); }
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 32;            // BK floats = 128 bytes = one swizzle row
+constexpr int STAGES = 2;
+constexpr int A_TILE_BYTES = BM * BK * 4;             // 16 KiB
+constexpr int B_TILE_BYTES = BN * BK * 4;             // 32 KiB
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // 96 KiB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 256;
+constexpr long long WAIT_CYCLES = 2000000000ll;        // bounded waits: about a second of SM clocks
+
+// Error word written by a kernel whose bounded wait ran out (0 = fine).
+__device__ unsigned int g_gemm_error;
+// Set by the split kernel when an operand holds inf/NaN (the split cannot represent those).
+__device__ unsigned int g_nonfinite_seen;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Returns false when the wait ran out of iterations.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const long long start = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - start > WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows are 128 bytes, 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+// kind::tf32, FP32 accumulate, A and B K-major, M=128, N=256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p; }"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(kInstrDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ float ref_relu(float v) {
+    return ((__float_as_uint(v) & 0x7fffffffu) == 0u) ? v : fmaxf(v, 0.0f);
+}
+__device__ __forceinline__ float ref_relu_vjp(float x, float g) {
+    const unsigned b = __float_as_uint(x), mag = b & 0x7fffffffu;
+    return (mag > 0x7f800000u || ((b >> 31) == 0u && mag != 0u)) ? g : 0.0f;
+}
+
+struct EpilogueArgs {
+    float* c;
+    const float* bias;
+    const float* aux;
+    float* preact;
+    long long c_batch_stride, c_row_stride;
+    int m, n, k_blocks, epilogue;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                   const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                   const EpilogueArgs e) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready; then the TMEM base word.
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y, batch = blockIdx.z;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[STAGES + s]), 1); }
+        mbar_init(smem_u32(&bars[2 * STAGES]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool failed = false;
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            for (int kb = 0; kb < e.k_blocks && !failed; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                if (round > 0 && !mbar_wait(smem_u32(&bars[STAGES + s]), (round - 1) & 1)) { failed = true; break; }
+                const uint32_t full = smem_u32(&bars[s]);
+                const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_3d(base, &map_a_hi, full, kb * BK, tile_m * BM, batch);
+                tma_load_3d(base + A_TILE_BYTES, &map_a_lo, full, kb * BK, tile_m * BM, batch);
+                tma_load_3d(base + 2 * A_TILE_BYTES, &map_b_hi, full, kb * BK, tile_n * BN, batch);
+                tma_load_3d(base + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full, kb * BK, tile_n * BN, batch);
+            }
+            if (failed) atomicExch(&g_gemm_error, 1u);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            for (int kb = 0; kb < e.k_blocks && !failed; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(smem_u32(&bars[s]), (kb / STAGES) & 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
+                const uint64_t b_hi = smem_desc(base + 2 * A_TILE_BYTES), b_lo = smem_desc(base + 2 * A_TILE_BYTES + B_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 8; ++k) {
+                    const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);      // 32 bytes per UMMA K step
+                    // small terms first, the dominant hi*hi product last
+                    umma_tf32(tmem_base, a_lo + step, b_hi + step, (kb | k) != 0);
+                    umma_tf32(tmem_base, a_hi + step, b_lo + step, 1u);
+                    umma_tf32(tmem_base, a_hi + step, b_hi + step, 1u);
+                }
+                umma_commit(smem_u32(&bars[STAGES + s]));                     // stage reusable once these MMAs retire
+            }
+            umma_commit(smem_u32(&bars[2 * STAGES]));                          // accumulator complete
+            if (failed) atomicExch(&g_gemm_error, 2u);
+        }
+    } else {
+        // ---- epilogue warps 2..5: TMEM lanes 32*(warp%4) .. +31 ----
+        const int quarter = warp & 3;
+        const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) {
+            if (lane == 0) atomicExch(&g_gemm_error, 3u);
+        } else {
+            const long long row = (long long)tile_m * BM + quarter * 32 + lane;
+            const long long batch_off = (long long)batch * e.c_batch_stride;
+            const bool vec_ok = (e.c_row_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.c) & 15u) == 0) && (e.c_batch_stride % 4 == 0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const long long col0 = (long long)tile_n * BN + c0;
+                if (row < e.m && col0 < e.n) {
+                    const long long idx0 = batch_off + row * e.c_row_stride + col0;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    const bool full_cols = col0 + 32 <= e.n;
+                    if (e.epilogue == TRS_EPI_BIAS || e.epilogue == TRS_EPI_BIAS_RELU) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (full_cols || col0 + j < e.n) v[j] = __fadd_rn(v[j], __ldg(e.bias + col0 + j));
+                    }
+                    if (e.epilogue == TRS_EPI_BIAS_RELU && e.preact) {
+                        if (full_cols && vec_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.preact + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.preact[idx0 + j] = v[j];
+                        }
+                    }
+                    if (e.epilogue == TRS_EPI_BIAS_RELU || e.epilogue == TRS_EPI_RELU) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = ref_relu(v[j]);
+                    }
+                    if (e.epilogue == TRS_EPI_RELU_VJP) {
+                        if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.aux) & 15u) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 z = __ldcs(reinterpret_cast<const float4*>(e.aux + idx0 + j));
+                                v[j] = ref_relu_vjp(z.x, v[j]); v[j + 1] = ref_relu_vjp(z.y, v[j + 1]);
+                                v[j + 2] = ref_relu_vjp(z.z, v[j + 2]); v[j + 3] = ref_relu_vjp(z.w, v[j + 3]);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
+                        }
+                    }
+                    if (full_cols && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.c[idx0 + j] = v[j];
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+// ---- operand preparation: strided f32 -> K-major hi / lo planes -------------------------------------
+
+struct SplitArgs {
+    const float* src;
+    float* hi;
+    float* lo;
+    long long batch_stride, row_stride, k_stride;     // source strides in elements
+    long long rows, k, k_pad;
+    unsigned int* nonfinite;
+};
+
+__device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsigned int* nonfinite) {
+    const uint32_t bits = __float_as_uint(a);
+    if ((bits & 0x7f800000u) == 0x7f800000u) {         // inf / NaN: not representable by the split
+        atomicOr(nonfinite, 1u);
+        hi = a; lo = 0.0f;
+        return;
+    }
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+    if ((h & 0x7f800000u) == 0x7f800000u) h = bits & 0xffffe000u;   // rounding overflowed: truncate instead
+    hi = __uint_as_float(h);
+    const float rest = __fsub_rn(a, hi);                // exact
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    lo = __uint_as_float(l);
+}
+
+// Source unit-stride along k: each thread converts 4 consecutive k of one row.
+__global__ void __launch_bounds__(256) split_tf32_kfast_kernel(const SplitArgs a, int vec) {
+    const long long quads = a.k_pad >> 2;
+    const long long total = a.rows * quads;
+    const long long batch = blockIdx.y;
+    const float* src = a.src + batch * a.batch_stride;
+    float* hi = a.hi + batch * a.rows * a.k_pad;
+    float* lo = a.lo + batch * a.rows * a.k_pad;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / quads, k0 = (i - r * quads) << 2;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* p = src + r * a.row_stride + k0;
+        if (vec && k0 + 4 <= a.k) {
+            const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) if (k0 + e < a.k) v[e] = __ldg(p + e);
+        }
+        float h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_value(v[e], h[e], l[e], a.nonfinite);
+        *reinterpret_cast<float4*>(hi + r * a.k_pad + k0) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lo + r * a.k_pad + k0) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// Any other source layout (unit stride along rows, or fully strided): 32x32 tiles through shared
+// memory, read along the rows axis, written along k.
+__global__ void __launch_bounds__(256) split_tf32_tiled_kernel(const SplitArgs a) {
+    __shared__ float tile[32][33];
+    const long long batch = blockIdx.z;
+    const float* src = a.src + batch * a.batch_stride;
+    float* hi = a.hi + batch * a.rows * a.k_pad;
+    float* lo = a.lo + batch * a.rows * a.k_pad;
+    const long long r0 = (long long)blockIdx.x * 32, k0 = (long long)blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const long long k = k0 + ty + 8 * j, r = r0 + tx;
+        tile[ty + 8 * j][tx] = (k < a.k && r < a.rows) ? __ldg(src + r * a.row_stride + k * a.k_stride) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const long long r = r0 + ty + 8 * j, k = k0 + tx;
+        if (r < a.rows && k < a.k_pad) {
+            float h, l;
+            split_value(tile[tx][ty + 8 * j], h, l, a.nonfinite);
+            hi[r * a.k_pad + k] = h;
+            lo[r * a.k_pad + k] = l;
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long k_pad, long long batch, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {(cuuint64_t)k_pad, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)k_pad * 4, (cuuint64_t)rows * (cuuint64_t)k_pad * 4};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TRS_OK;
+}
+
+struct DeviceWords {
+    unsigned int* error = nullptr;
+    unsigned int* nonfinite = nullptr;
+    bool launched = false;
+    bool smem_set = false;
+};
+DeviceWords g_words[16];
+std::mutex g_words_mu;
+
+int32_t device_words(int device, DeviceWords** out) {
+    std::lock_guard<std::mutex> lock(g_words_mu);
+    DeviceWords& w = g_words[device];
+    if (!w.error) {
+        TRS_CUDA(cudaGetSymbolAddress((void**)&w.error, g_gemm_error));
+        TRS_CUDA(cudaGetSymbolAddress((void**)&w.nonfinite, g_nonfinite_seen));
+    }
+    if (!w.smem_set) {
+        TRS_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        w.smem_set = true;
+    }
+    *out = &w;
+    return TRS_OK;
+}
+
+int32_t launch_split(const float* src, long long batch, long long rows, long long k, long long k_pad, long long batch_stride,
+                     long long row_stride, long long k_stride, float* hi, float* lo, unsigned int* nonfinite, trs_stream stream) {
+    SplitArgs a{src, hi, lo, batch_stride, row_stride, k_stride, rows, k, k_pad, nonfinite};
+    if (k_stride == 1 || k == 1) {
+        const int vec = (row_stride % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+        const long long total = rows * (k_pad >> 2);
+        unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)sm_count(stream->device) * 32);
+        split_tf32_kfast_kernel<<<dim3(std::max(grid, 1u), (unsigned)batch), 256, 0, stream->stream>>>(a, vec);
+    } else {
+        dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(k_pad / 32), (unsigned)batch);
+        split_tf32_tiled_kernel<<<grid, 256, 0, stream->stream>>>(a);
+    }
+    TRS_CUDA(cudaGetLastError());
+    count_launch();
+    return TRS_OK;
+}
+
+}  // namespace
+
+bool gemm_tc_eligible(const trs_gemm_desc& g) {
+    if (g.batch < 1 || g.batch > 65535 || g.k < 32 || g.m < 1 || g.n < 1) return false;
+    if ((g.m + BM - 1) / BM > 65535) return false;
+    // Small problems stay on the exact-FP32 SIMT kernel: the split's two extra passes do not pay off.
+    return (double)g.m * (double)g.n * (double)g.k >= (double)(1 << 21);
+}
+
+size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g) {
+    const long long k_pad = (g.k + BK - 1) / BK * BK;
+    return (size_t)(2 * g.batch * (g.m + g.n) * k_pad) * sizeof(float);
+}
+
+// Runs split + GEMM with caller-provided scratch of gemm_tc_scratch_bytes(g).
+int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream stream) {
+    DeviceWords* words = nullptr;
+    TRS_TRY(device_words(stream->device, &words));
+    const long long k_pad = (g.k + BK - 1) / BK * BK;
+    const long long a_plane = g.batch * g.m * k_pad, b_plane = g.batch * g.n * k_pad;
+    float* a_hi = scratch;
+    float* a_lo = a_hi + a_plane;
+    float* b_hi = a_lo + a_plane;
+    float* b_lo = b_hi + b_plane;
+    TRS_CUDA(cudaMemsetAsync(words->nonfinite, 0, sizeof(unsigned int), stream->stream));
+    // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
+    TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream));
+    TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream));
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM));
+    TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM));
+    TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, BN));
+    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, BN));
+    EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / BK), g.epilogue};
+    dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
+    gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
+    TRS_CUDA(cudaGetLastError());
+    count_launch();
+    words->launched = true;
+    // inf / NaN operands: recompute with the exact-FP32 kernel (a no-op launch when none were seen),
+    // which keeps the reference's inf/NaN classification of the result.
+    TRS_TRY(gemm_simt_launch(g, stream, words->nonfinite));
+    return TRS_OK;
+}
+
+int32_t gemm_tc_launch(const trs_gemm_desc& g, trs_stream stream) {
+    if (g.m > INT32_MAX || g.n > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "matrix extent above 2^31");
+    void* scratch = nullptr;
+    TRS_TRY(trs_malloc(stream->device, gemm_tc_scratch_bytes(g), &scratch));
+    int32_t s = gemm_tc_launch_ws(g, (float*)scratch, stream);
+    trs_free(stream->device, scratch);       // reuse is ordered behind this stream's work
+    return s;
+}
+
+// Reads (and clears) the error word of kernels with bounded waits; called after a stream or device sync.
+int32_t gemm_check_status(int device) {
+    DeviceWords& w = g_words[device];
+    if (!w.launched || !w.error) return TRS_OK;
+    unsigned int value = 0;
+    TRS_CUDA(cudaMemcpy(&value, w.error, sizeof value, cudaMemcpyDeviceToHost));
+    w.launched = false;
+    if (value != 0) {
+        unsigned int zero = 0;
+        cudaMemcpy(w.error, &zero, sizeof zero, cudaMemcpyHostToDevice);
+        return fail(TRS_ERR_DEVICE_STATUS, "tensor-core matmul: a bounded wait ran out (stage %u); the result is invalid", value);
+    }
+    return TRS_OK;
+}
+
 }  // namespace trs

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "common.h"
+#include "gemm.h"
 
 namespace trs {
 thread_local std::string g_last_error;
@@ -176,7 +177,7 @@ int32_t trs_stream_destroy(trs_stream stream) {
 int32_t trs_stream_sync(trs_stream stream) {
     TRS_TRY(check_stream(stream));
     TRS_CUDA(cudaStreamSynchronize(stream->stream));
-    return TRS_OK;
+    return gemm_check_status(stream->device);
 }
 
 int32_t trs_stream_device(trs_stream stream, int32_t* device) {
@@ -195,7 +196,7 @@ int32_t trs_device_sync(int32_t device) {
     DeviceGuard guard(device);
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     TRS_CUDA(cudaDeviceSynchronize());
-    return TRS_OK;
+    return gemm_check_status(device);
 }
 
 int32_t trs_event_create(trs_event* event) {

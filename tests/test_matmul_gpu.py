@@ -16,7 +16,18 @@ from tests.test_oracle_golden import build_operand
 
 pytestmark = pytest.mark.gpu
 GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
-ALGOS = ["simt_fp32", "auto"]
+ALGOS = ["simt_fp32", "tcgen05_3xtf32", "auto"]
+
+
+def run(a, b, algo, **kw):
+    """run_matmul, skipping shapes the requested algorithm does not take."""
+    from torch_rs._abi import TrsError
+    try:
+        return run_matmul(a, b, algo=algo, **kw)
+    except TrsError as err:
+        if err.status == 5:
+            pytest.skip("shape not eligible for " + algo)
+        raise
 
 
 def rnd(seed, *shape, scale=1.0):
@@ -27,7 +38,7 @@ def rnd(seed, *shape, scale=1.0):
 def test_reference_goldens_exact(algo):
     for case in GOLD["matmul"]["cases"]:
         a, b = build_operand(case["left"]), build_operand(case["right"])
-        c, _ = run_matmul(a, b, algo=algo)
+        c, _ = run(a, b, algo)
         assert c.reshape(-1).tolist() == case["expected"], case["source"]
 
 
@@ -36,7 +47,7 @@ def test_reference_goldens_exact(algo):
 def test_contiguous_matches_checker(algo, m, n, k):
     a, b = RefTensor.from_numpy(rnd(0, m, k)), RefTensor.from_numpy(rnd(1, k, n, scale=1 / np.sqrt(k)))
     expected = a.matmul(b).logical()
-    c, _ = run_matmul(a, b, algo=algo)
+    c, _ = run(a, b, algo)
     ok, worst = matmul_tolerance_ok(c, expected, k)
     assert ok, f"worst error/bound {worst}"
 
@@ -47,7 +58,7 @@ def test_transposed_and_offset_views(algo):
     at = RefTensor.from_numpy(rnd(2, k, m)).mT                  # A read through .mT (m contiguous)
     bt = RefTensor.from_numpy(rnd(3, 2, n, k)).select0(1).mT    # offset + transposed B (k contiguous)
     expected = at.matmul(bt).logical()
-    c, _ = run_matmul(at, bt, algo=algo)
+    c, _ = run(at, bt, algo)
     ok, worst = matmul_tolerance_ok(c, expected, k)
     assert ok, worst
 
@@ -59,7 +70,7 @@ def test_batched_bias_relu_epilogue_matches_composition(algo):
     x = RefTensor.from_numpy(rnd(4, batch, m, k))
     w = RefTensor.from_numpy(rnd(5, batch, n, k, scale=1 / 32))
     bias = np.random.default_rng(6).uniform(-0.1, 0.1, n).astype(np.float32)
-    c, pre = run_matmul(x, w.mT, bias=bias, epilogue="bias_relu", want_preact=True, algo=algo)
+    c, pre = run(x, w.mT, algo, bias=bias, epilogue="bias_relu", want_preact=True)
     for i in range(batch):
         z = x.select0(i).matmul(w.select0(i).mT) + RefTensor(bias, [n])
         ok, worst = matmul_tolerance_ok(pre[i], z.logical(), k)
@@ -74,7 +85,7 @@ def test_relu_vjp_epilogue(algo):
     m, n, k = 256, 128, 64
     dy, w2 = RefTensor.from_numpy(rnd(7, m, k)), RefTensor.from_numpy(rnd(8, n, k))
     z = rnd(9, m, n)
-    c, _ = run_matmul(dy, w2.mT, epilogue="relu_vjp", aux=z, algo=algo)
+    c, _ = run(dy, w2.mT, algo, epilogue="relu_vjp", aux=z)
     dh = dy.matmul(w2.mT).logical()
     mask = (z > 0) | np.isnan(z)
     ok, worst = matmul_tolerance_ok(c, np.where(mask, dh, 0.0), k)
@@ -86,3 +97,33 @@ def test_empty_and_zero_inner():
     a, b = RefTensor(np.zeros(0, dtype=np.float32), [4, 0]), RefTensor(np.zeros(0, dtype=np.float32), [0, 3])
     c, _ = run_matmul(a, b)
     assert c.shape == (4, 3) and np.all(c == 0.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 32), (129, 257, 40), (300, 520, 100), (1024, 768, 2048), (64, 64, 4096)])
+def test_tensor_core_path_odd_shapes_and_k_tails(m, n, k):
+    a, b = RefTensor.from_numpy(rnd(20, m, k)), RefTensor.from_numpy(rnd(21, k, n, scale=1 / np.sqrt(k)))
+    c, _ = run(a, b, "tcgen05_3xtf32")
+    ok, worst = matmul_tolerance_ok(c, a.matmul(b).logical(), k)
+    assert ok, f"worst error/bound {worst}"
+    # tighter than the stated tolerance: the 3-product split keeps ~2^-21 relative accuracy per product
+    ref64 = a.logical().astype(np.float64) @ b.logical().astype(np.float64)
+    rms = np.sqrt(np.mean(ref64 ** 2))
+    assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * rms
+
+
+def test_tensor_core_path_keeps_inf_nan_classification():
+    # The reference's differential tests classify inf / NaN / sign of matmul results
+    # (tests/test_matmul_reference.py:43-50); non-finite operands reroute to the exact-FP32 kernel.
+    m, n, k = 128, 256, 64
+    a, b = rnd(22, m, k), rnd(23, k, n)
+    a[3, 5] = np.inf
+    a[70, 9] = np.nan
+    b[9, 200] = -np.inf
+    ra, rb = RefTensor.from_numpy(a), RefTensor.from_numpy(b)
+    c, _ = run(ra, rb, "tcgen05_3xtf32")
+    want = ra.matmul(rb).logical()
+    assert np.array_equal(np.isnan(c), np.isnan(want))
+    assert np.array_equal(np.isinf(c), np.isinf(want))
+    finite = np.isfinite(want)
+    assert np.array_equal(np.sign(c[np.isinf(want)]), np.sign(want[np.isinf(want)]))
+    assert np.allclose(c[finite], want[finite], rtol=1e-4, atol=1e-4)
