@@ -183,6 +183,18 @@ int32_t trs_reduce_sum_f32(const trs_operand* input, float* out, trs_stream stre
 int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, int32_t by_rows, float* out,
                                 trs_stream stream);
 
+/* Column sums without any allocation: out[j] = sum over r of input[r*cols + j], the same result as
+ * trs_unbroadcast_sum_f32(..., by_rows = 0, ...).  No counterpart in the reference; it exists for
+ * callers that cannot allocate device memory at the point of the call (a stream being captured, a
+ * driver callback, a service whose memory pool is fixed after start-up).  The partial sums live in a
+ * fixed 1 MiB array inside the library (held on every GPU that loads it, until exit), so `cols` may be
+ * at most 262144; larger requests fail with TRS_ERR_UNSUPPORTED.  It calls no cudaMalloc / cudaFree
+ * and no allocating library routine.  The first call on each device resolves the array's device
+ * address (once); make that call before starting any stream capture.  All calls share the one
+ * array: two calls whose kernels can overlap on the GPU (different streams) race and must be ordered
+ * by the caller.  Nothing has to be cleared between calls. */
+int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, float* out, trs_stream stream);
+
 /* ---- matmul ----------------------------------------------------------------------------------
  * Honours float32 matmul precision "highest" (python/torch_rs/__init__.py:81-85): either exact
  * FP32 FMA accumulation or the 3xTF32 error-compensated split with FP32 accumulation. */

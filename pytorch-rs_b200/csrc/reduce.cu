@@ -265,4 +265,54 @@ int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, 
     return s;
 }
 
+
+// ---- column sums for callers that must not allocate ---------------------------------------------
+// Some hosts of this library run where a device allocation is not an option: inside a region that
+// is being stream-captured, inside a callback that the driver runs, or in a service that sized its
+// memory pool at start-up and forbids growth afterwards.  For them the stage-1 partials live in a
+// fixed array that is part of the library image: 1 MiB per GPU that loads the library, held until
+// the process exits.
+constexpr long long kNoAllocScratchFloats = 262144;      // 1 MiB; also the largest `cols` accepted
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+static float* g_noalloc_scratch_ptr[16];                  // device address per device, resolved once
+
+int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, float* out, trs_stream stream) {
+    TRS_TRY(check_stream(stream));
+    if (rows < 0 || cols < 0) return fail(TRS_ERR_INVALID_ARGUMENT, "negative extent");
+    if (!out || (!input && rows * cols != 0)) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (cols > kNoAllocScratchFloats)
+        return fail(TRS_ERR_UNSUPPORTED, "trs_colsum_f32_noalloc: %lld columns exceed the fixed scratch of %lld floats; "
+                                         "use trs_unbroadcast_sum_f32", (long long)cols, kNoAllocScratchFloats);
+    const int device = stream->device;
+    if (device < 0 || device >= 16) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
+    if (cols == 0) return TRS_OK;
+    // The array's name is only a host-side handle; the kernels need its address on THIS device.
+    if (!g_noalloc_scratch_ptr[device]) {
+        float* ptr = nullptr;
+        cudaError_t err = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess) return cuda_fail(err, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        g_noalloc_scratch_ptr[device] = ptr;
+    }
+    float* scratch = g_noalloc_scratch_ptr[device];
+    if (rows == 0) { fill_value_async(out, cols, 0.0f, stream); return TRS_OK; }
+    int chunks = 0;
+    long long rows_per_chunk = 0;
+    colsum_geometry(device, rows, cols, &chunks, &rows_per_chunk);
+    const long long fit = kNoAllocScratchFloats / cols;       // >= 1 because cols <= the scratch size
+    if (chunks > fit) {
+        rows_per_chunk = (rows + fit - 1) / fit;
+        chunks = (int)((rows + rows_per_chunk - 1) / rows_per_chunk);
+    }
+    const int vec = (cols % 4 == 0) && (((uintptr_t)input & 15u) == 0);
+    dim3 grid((unsigned)((cols + 127) / 128), (unsigned)chunks);
+    // Stage 1 writes every partial that stage 2 reads, so nothing left by an earlier call matters.
+    colsum_stage1<<<grid, kBlock, 0, stream->stream>>>(input, rows, cols, rows_per_chunk, scratch, vec);
+    colsum_stage2<<<(unsigned)((cols + kBlock - 1) / kBlock), kBlock, 0, stream->stream>>>(scratch, chunks, cols, out);
+    TRS_CUDA(cudaGetLastError());
+    count_launch(2);
+    return TRS_OK;
+}
+
 }  // extern "C"

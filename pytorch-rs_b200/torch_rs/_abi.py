@@ -85,6 +85,7 @@ _PROTOTYPES = {
     "trs_reduce_sum_f32": [ctypes.POINTER(Operand), ctypes.c_void_p, ctypes.c_void_p],
     "trs_unbroadcast_sum_f32": [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
                                 ctypes.c_void_p],
+    "trs_colsum_f32_noalloc": [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p],
     "trs_matmul_f32": [ctypes.POINTER(GemmDesc), ctypes.c_void_p],
     "trs_matmul_select_algo": [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_int32)],
     "trs_jit_cache_size": [ctypes.POINTER(ctypes.c_int32)],
