@@ -335,12 +335,117 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+WORKLOADS = {
+    "c1": "relu(x + y), x,y f32 [4096,4096] contiguous ~U(-1,1); 4 rotating operand sets defeat L2",
+    "c3": "matmul(A, B), f32 [4096,4096]^2 ~N(0,1/64), precision highest",
+    "c4": "relu(X @ W.mT + bias), X,W f32 [64,1024,1024], bias [1024]; batches sharded over ranks",
+    "c5": "2-layer MLP forward+backward, X f32 [65536,4096], W1 [4096,4096], W2 [4096,1024], b1 [4096]; "
+          "rows of X sharded over ranks, NCCL all-reduce of the W1/W2/b1 gradients",
+}
+
+
+def run_side_workload(args, rank, world, local_rank):
+    """The other BASELINE configs (not the headline line): same timing rules, one JSON line on rank 0."""
+    import ctypes
+    import torch_rs as torch
+    from torch_rs import _host, distributed as tdist
+    from torch_rs._device import Stream, launch_count
+    if world > 1:
+        tdist.init_process_group("nccl")
+    dev = f"cuda:{local_rank}"
+    raw = ctypes.c_void_p()
+    _host.check(_host.lib().trsh_stream(local_rank, ctypes.byref(raw)))
+    stream = Stream.__new__(Stream)
+    stream.device, stream.handle = local_rank, raw
+    rng = np.random.default_rng(rank)
+    held = [None]
+    name = args.workload
+    hbm_peak, peak_kind, peaks = measured_peaks()
+    tensor_peak = float(peaks.get("bf16_tflops", 1590.0)) / 6.0     # tf32 runs at half the bf16 rate; 3 MMAs per product
+    if name == "c1":
+        n = 4096
+        sets = [(torch.tensor(rng.uniform(-1, 1, (n, n)).astype(np.float32), device=dev),
+                 torch.tensor(rng.uniform(-1, 1, (n, n)).astype(np.float32), device=dev)) for _ in range(4)]
+        it = [0]
+
+        def step():
+            xa, ya = sets[it[0] % 4]
+            it[0] += 1
+            held[0] = torch.relu(xa + ya).materialize()
+        work, unit, metric, bound, peak = 12 * n * n * world, "GB/s", "fused pointwise GB/s", "hbm", hbm_peak
+        scale, scaling = 1e9, "weak"
+    elif name == "c3":
+        n = 4096
+        a = torch.tensor((rng.standard_normal((n, n)) / 64).astype(np.float32), device=dev)
+        b = torch.tensor((rng.standard_normal((n, n)) / 64).astype(np.float32), device=dev)
+
+        def step():
+            held[0] = torch.matmul(a, b).materialize()
+        work, unit, metric, bound, peak = 2 * n ** 3 * world, "TFLOP/s", "f32 matmul TFLOP/s", "tensor", tensor_peak
+        scale, scaling = 1e12, "weak"
+    elif name == "c4":
+        lo, hi = tdist.shard_bounds(64, rank, world)
+        nb = hi - lo
+        X = torch.tensor(rng.standard_normal((nb, 1024, 1024)).astype(np.float32), device=dev)
+        W = torch.tensor((rng.standard_normal((nb, 1024, 1024)) / 32).astype(np.float32), device=dev)
+        bias = torch.tensor(rng.uniform(-0.1, 0.1, 1024).astype(np.float32), device=dev)
+
+        def step():
+            held[0] = torch.relu(X @ W.mT + bias).materialize()
+        work, unit, metric, bound, peak = 64 * 2 * 1024 ** 3, "TFLOP/s", "f32 bmm+bias+relu TFLOP/s", "tensor", tensor_peak
+        scale, scaling = 1e12, "strong"
+    else:
+        lo, hi = tdist.shard_bounds(65536, rank, world)
+        X = torch.tensor(rng.standard_normal((hi - lo, 4096)).astype(np.float32), device=dev)
+        shared = np.random.default_rng(0)
+        w1 = torch.tensor((shared.standard_normal((4096, 4096)) / 64).astype(np.float32), device=dev)
+        w2 = torch.tensor((shared.standard_normal((4096, 1024)) / 64).astype(np.float32), device=dev)
+        b1 = torch.zeros(4096, device=dev)
+
+        def step():
+            W1, W2, B1 = w1.detach().requires_grad_(), w2.detach().requires_grad_(), b1.detach().requires_grad_()
+            loss = (torch.relu(X @ W1 + B1) @ W2).sum()
+            loss.backward()
+            tdist.all_reduce_gradients((W1, W2, B1))
+            held[0] = (loss, W1.grad, W2.grad, B1.grad)
+        work, unit, metric, bound, peak = 2 * 65536 * (2 * 4096 ** 2 + 3 * 4096 * 1024), "TFLOP/s", "MLP fwd+bwd TFLOP/s", "tensor", tensor_peak
+        scale, scaling = 1e12, "strong"
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.synchronize(local_rank)
+    tdist.barrier()
+    launches0 = launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ms = time_region(stream, step, args.steps)
+        launches = launch_count() - launches0
+        torch.synchronize(local_rank)
+    ms = float(tdist.all_reduce_host(np.array([ms]), op="max")[0])
+    tdist.barrier()
+    if world > 1:
+        tdist.destroy_process_group()
+    if rank != 0:
+        return
+    ms_per_step = ms / args.steps
+    value = work / (ms_per_step * 1e-3) / scale
+    per_gpu = value / world
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOADS[name], "parallelism": f"dp{world}"},
+            "roofline": {"bound": bound, "achieved": per_gpu, "peak": peak, "unit": unit, "frac": per_gpu / peak, "traffic": None,
+                         "peak_source": f"of {peak_kind}" + (" (bf16_tflops / 6: tf32 at half rate, 3 MMAs per product)" if bound == "tensor" else "")},
+            "gpu_launches": launches, "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="c2 (default) is the headline fused chain; the others are BASELINE's remaining configs")
     ap.add_argument("--no-extra", action="store_true", help="skip the relu(x+y) and matmul side figures")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -352,6 +457,9 @@ def main():
         return
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    if args.workload != "c2":
+        run_side_workload(args, rank, world, local_rank)
+        return
     run_ours(args, rank, world, local_rank)
 
 

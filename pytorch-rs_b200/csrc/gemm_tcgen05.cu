@@ -27,14 +27,17 @@
 namespace trs {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 32;            // BK floats = 128 bytes = one swizzle row
-constexpr int STAGES = 2;
-constexpr int A_TILE_BYTES = BM * BK * 4;             // 16 KiB
-constexpr int B_TILE_BYTES = BN * BK * 4;             // 32 KiB
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // 96 KiB
+constexpr int BM = 128, BN = 256;
+constexpr int BK = 16;                                // floats per pipeline stage along K (16 -> 64-byte swizzle rows, 32 -> 128-byte)
+constexpr int STAGES = BK == 16 ? 4 : 2;
+constexpr int ROW_BYTES = BK * 4;
+constexpr int A_TILE_BYTES = BM * ROW_BYTES;
+constexpr int B_TILE_BYTES = BN * ROW_BYTES;
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // 48 KiB (BK=16) or 96 KiB (BK=32)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int TMEM_COLS = 256;
+constexpr int TMEM_COLS = 512;                        // two 128x256 FP32 accumulators
 constexpr long long WAIT_CYCLES = 2000000000ll;        // bounded waits: about a second of SM clocks
+constexpr int K_PAD = 32;                             // operand planes are padded along K to this many floats
 
 // Error word written by a kernel whose bounded wait ran out (0 = fine).
 __device__ unsigned int g_gemm_error;
@@ -65,14 +68,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
-// K-major operand tile with 128-byte swizzle: rows are 128 bytes, 8-row groups are 1024 bytes apart.
+// K-major operand tile whose rows are one swizzle span (128 or 64 bytes): 8-row groups are
+// 8 * ROW_BYTES apart; layout type 2 = SWIZZLE_128B, 4 = SWIZZLE_64B.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride between 8-row groups
+    d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;       // stride between 8-row groups
     d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    d |= (uint64_t)(ROW_BYTES == 128 ? 2 : 4) << 61;
     return d;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // kind::tf32, FP32 accumulate, A and B K-major, M=128, N=256.
@@ -101,8 +108,26 @@ struct EpilogueArgs {
     float* preact;
     long long c_batch_stride, c_row_stride;
     int m, n, k_blocks, epilogue;
+    int tiles_m, tiles_n, total_tiles;
 };
 
+// Tile order: bands of 16 tile rows, walked column by column, so that the ~148 tiles in flight at
+// any time cover a roughly square 16 x 9 patch of C and share their A and B panels in L2.
+constexpr int GROUP_M = 16;
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& batch, int& tile_m, int& tile_n) {
+    const int per_batch = tiles_m * tiles_n;
+    batch = t / per_batch;
+    const int rem = t - batch * per_batch;
+    const int band = rem / (GROUP_M * tiles_n);
+    const int first_m = band * GROUP_M;
+    const int band_rows = min(GROUP_M, tiles_m - first_m);
+    const int in_band = rem - band * GROUP_M * tiles_n;
+    tile_n = in_band / band_rows;
+    tile_m = first_m + (in_band - tile_n * band_rows);
+}
+
+// Persistent kernel: CTA i works on tiles i, i + gridDim.x, ...; the accumulator of tile j lives
+// in TMEM columns (j & 1) * 256, so the epilogue of one tile overlaps the MMAs of the next.
 __global__ void __launch_bounds__(192, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
@@ -110,14 +135,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready; then the TMEM base word.
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    // bars: [0,S) stage full, [S,2S) stage empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y, batch = blockIdx.z;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[STAGES + s]), 1); }
-        mbar_init(smem_u32(&bars[2 * STAGES]), 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -130,62 +158,83 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    bool failed = false;
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ----
-            for (int kb = 0; kb < e.k_blocks && !failed; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (round > 0 && !mbar_wait(smem_u32(&bars[STAGES + s]), (round - 1) & 1)) { failed = true; break; }
-                const uint32_t full = smem_u32(&bars[s]);
-                const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
-                mbar_expect_tx(full, STAGE_BYTES);
-                tma_load_3d(base, &map_a_hi, full, kb * BK, tile_m * BM, batch);
-                tma_load_3d(base + A_TILE_BYTES, &map_a_lo, full, kb * BK, tile_m * BM, batch);
-                tma_load_3d(base + 2 * A_TILE_BYTES, &map_b_hi, full, kb * BK, tile_n * BN, batch);
-                tma_load_3d(base + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full, kb * BK, tile_n * BN, batch);
+            bool failed = false;
+            uint32_t g = 0;                                           // stage uses so far, over all tiles
+            for (int t = blockIdx.x; t < e.total_tiles && !failed; t += gridDim.x) {
+                int batch, tile_m, tile_n;
+                decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
+                for (int kb = 0; kb < e.k_blocks; ++kb, ++g) {
+                    const uint32_t s = g % STAGES, round = g / STAGES;
+                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1)) { failed = true; break; }
+                    const uint32_t full = smem_u32(&full_bar[s]);
+                    const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_3d(base, &map_a_hi, full, kb * BK, tile_m * BM, batch);
+                    tma_load_3d(base + A_TILE_BYTES, &map_a_lo, full, kb * BK, tile_m * BM, batch);
+                    tma_load_3d(base + 2 * A_TILE_BYTES, &map_b_hi, full, kb * BK, tile_n * BN, batch);
+                    tma_load_3d(base + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full, kb * BK, tile_n * BN, batch);
+                }
             }
             if (failed) atomicExch(&g_gemm_error, 1u);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ----
-            for (int kb = 0; kb < e.k_blocks && !failed; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(smem_u32(&bars[s]), (kb / STAGES) & 1)) { failed = true; break; }
+            bool failed = false;
+            uint32_t g = 0, it = 0;
+            for (int t = blockIdx.x; t < e.total_tiles && !failed; t += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, use = it >> 1;
+                // the epilogue must have drained this accumulator's previous tile
+                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
-                const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
-                const uint64_t b_hi = smem_desc(base + 2 * A_TILE_BYTES), b_lo = smem_desc(base + 2 * A_TILE_BYTES + B_TILE_BYTES);
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = 0; kb < e.k_blocks; ++kb, ++g) {
+                    const uint32_t s = g % STAGES;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / STAGES) & 1)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
+                    const uint64_t b_hi = smem_desc(base + 2 * A_TILE_BYTES), b_lo = smem_desc(base + 2 * A_TILE_BYTES + B_TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 8; ++k) {
-                    const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);      // 32 bytes per UMMA K step
-                    // small terms first, the dominant hi*hi product last
-                    umma_tf32(tmem_base, a_lo + step, b_hi + step, (kb | k) != 0);
-                    umma_tf32(tmem_base, a_hi + step, b_lo + step, 1u);
-                    umma_tf32(tmem_base, a_hi + step, b_hi + step, 1u);
+                    for (int k = 0; k < BK / 8; ++k) {
+                        const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);      // 32 bytes per UMMA K step
+                        // small terms first, the dominant hi*hi product last
+                        umma_tf32(d, a_lo + step, b_hi + step, (kb | k) != 0);
+                        umma_tf32(d, a_hi + step, b_lo + step, 1u);
+                        umma_tf32(d, a_hi + step, b_hi + step, 1u);
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));                         // stage reusable once these MMAs retire
                 }
-                umma_commit(smem_u32(&bars[STAGES + s]));                     // stage reusable once these MMAs retire
+                umma_commit(smem_u32(&acc_full[acc]));                            // accumulator complete (or abandoned)
             }
-            umma_commit(smem_u32(&bars[2 * STAGES]));                          // accumulator complete
             if (failed) atomicExch(&g_gemm_error, 2u);
         }
     } else {
         // ---- epilogue warps 2..5: TMEM lanes 32*(warp%4) .. +31 ----
         const int quarter = warp & 3;
-        const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!ok) {
-            if (lane == 0) atomicExch(&g_gemm_error, 3u);
-        } else {
+        const bool vec_ok = (e.c_row_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.c) & 15u) == 0) && (e.c_batch_stride % 4 == 0) &&
+                            (!e.preact || (reinterpret_cast<uintptr_t>(e.preact) & 15u) == 0);
+        uint32_t it = 0;
+        bool failed = false;
+        for (int t = blockIdx.x; t < e.total_tiles && !failed; t += gridDim.x, ++it) {
+            int batch, tile_m, tile_n;
+            decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
+            const uint32_t acc = it & 1, use = it >> 1;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1)) {
+                if (lane == 0) atomicExch(&g_gemm_error, 3u);
+                failed = true;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long row = (long long)tile_m * BM + quarter * 32 + lane;
             const long long batch_off = (long long)batch * e.c_batch_stride;
-            const bool vec_ok = (e.c_row_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.c) & 15u) == 0) && (e.c_batch_stride % 4 == 0);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -196,6 +245,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c0 + 32 == BN) {
+                    // every column of this accumulator has been read into registers: hand it back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+                }
                 const long long col0 = (long long)tile_n * BN + c0;
                 if (row < e.m && col0 < e.n) {
                     const long long idx0 = batch_off + row * e.c_row_stride + col0;
@@ -359,9 +413,10 @@ int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long
     cuuint64_t dims[3] = {(cuuint64_t)k_pad, (cuuint64_t)rows, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)k_pad * 4, (cuuint64_t)rows * (cuuint64_t)k_pad * 4};
     cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    const CUtensorMapSwizzle swizzle = ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return TRS_OK;
 }
@@ -399,7 +454,7 @@ int32_t launch_split(const float* src, long long batch, long long rows, long lon
         unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)sm_count(stream->device) * 32);
         split_tf32_kfast_kernel<<<dim3(std::max(grid, 1u), (unsigned)batch), 256, 0, stream->stream>>>(a, vec);
     } else {
-        dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(k_pad / 32), (unsigned)batch);
+        dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(k_pad / 32), (unsigned)batch);   // k_pad is a multiple of 32
         split_tf32_tiled_kernel<<<grid, 256, 0, stream->stream>>>(a);
     }
     TRS_CUDA(cudaGetLastError());
@@ -417,7 +472,7 @@ bool gemm_tc_eligible(const trs_gemm_desc& g) {
 }
 
 size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g) {
-    const long long k_pad = (g.k + BK - 1) / BK * BK;
+    const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
     return (size_t)(2 * g.batch * (g.m + g.n) * k_pad) * sizeof(float);
 }
 
@@ -425,7 +480,7 @@ size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g) {
 int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream stream) {
     DeviceWords* words = nullptr;
     TRS_TRY(device_words(stream->device, &words));
-    const long long k_pad = (g.k + BK - 1) / BK * BK;
+    const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
     const long long a_plane = g.batch * g.m * k_pad, b_plane = g.batch * g.n * k_pad;
     float* a_hi = scratch;
     float* a_lo = a_hi + a_plane;
@@ -440,8 +495,12 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM));
     TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, BN));
     TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, BN));
-    EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / BK), g.epilogue};
-    dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
+    const long long tiles_m = (g.m + BM - 1) / BM, tiles_n = (g.n + BN - 1) / BN;
+    const long long total_tiles = tiles_m * tiles_n * g.batch;
+    if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
+    EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / BK), g.epilogue,
+                   (int)tiles_m, (int)tiles_n, (int)total_tiles};
+    const unsigned grid = (unsigned)std::min<long long>(total_tiles, sm_count(stream->device));
     gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
     TRS_CUDA(cudaGetLastError());
     count_launch();
