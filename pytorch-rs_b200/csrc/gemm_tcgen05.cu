@@ -388,6 +388,39 @@ __global__ void __launch_bounds__(256) split_tf32_tiled_kernel(const SplitArgs a
     }
 }
 
+// Source unit-stride along rows (a transposed view) and 16-byte aligned: 64x64 tiles, float4 reads
+// along rows, float4 hi/lo writes along k.
+__global__ void __launch_bounds__(256) split_tf32_tiled64_kernel(const SplitArgs a) {
+    __shared__ float tile[64][65];                       // [k][row]
+    const long long batch = blockIdx.z;
+    const float* src = a.src + batch * a.batch_stride;
+    float* hi = a.hi + batch * a.rows * a.k_pad;
+    float* lo = a.lo + batch * a.rows * a.k_pad;
+    const long long r0 = (long long)blockIdx.x * 64, k0 = (long long)blockIdx.y * 64;
+    const int q4 = (threadIdx.x & 15) * 4, r16 = threadIdx.x >> 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int kl = r16 + 16 * j;
+        const long long k = k0 + kl, r = r0 + q4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < a.k && r < a.rows) v = __ldcs(reinterpret_cast<const float4*>(src + k * a.k_stride + r));
+        tile[kl][q4] = v.x; tile[kl][q4 + 1] = v.y; tile[kl][q4 + 2] = v.z; tile[kl][q4 + 3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int rl = r16 + 16 * j;
+        const long long r = r0 + rl, k = k0 + q4;
+        if (r < a.rows && k < a.k_pad) {
+            float h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_value(tile[q4 + e][rl], h[e], l[e], a.nonfinite);
+            *reinterpret_cast<float4*>(hi + r * a.k_pad + k) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4*>(lo + r * a.k_pad + k) = make_float4(l[0], l[1], l[2], l[3]);
+        }
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -453,6 +486,11 @@ int32_t launch_split(const float* src, long long batch, long long rows, long lon
         const long long total = rows * (k_pad >> 2);
         unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)sm_count(stream->device) * 32);
         split_tf32_kfast_kernel<<<dim3(std::max(grid, 1u), (unsigned)batch), 256, 0, stream->stream>>>(a, vec);
+    } else if (row_stride == 1 && rows % 4 == 0 && k_stride % 4 == 0 && batch_stride % 4 == 0 &&
+               (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((k_pad + 63) / 64), (unsigned)batch);
+        if (grid.y > 65535) return fail(TRS_ERR_UNSUPPORTED, "inner dimension too large for the operand split");
+        split_tf32_tiled64_kernel<<<grid, 256, 0, stream->stream>>>(a);
     } else {
         dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(k_pad / 32), (unsigned)batch);   // k_pad is a multiple of 32
         split_tf32_tiled_kernel<<<grid, 256, 0, stream->stream>>>(a);

@@ -37,6 +37,7 @@ struct PwPlan {
     bool wide_offsets = false;   // some element offset needs more than 31 bits
     bool wide_items = false;     // work-item count needs more than 31 bits
     bool has_tail = false;       // inner size not a multiple of the vector width
+    bool tile_vec = false;       // tiled class: 64x64 tiles moved with 128-bit accesses (else 32x32 scalar)
     int unroll = 4;
     int block = 256;
     unsigned long long grid = 0;
