@@ -112,6 +112,22 @@ int32_t pw_make_plan(const trs_program* prog, const trs_operand* inputs, const t
     for (int k = 0; k < n_in; ++k) if (!inputs[k].base) return fail(TRS_ERR_INVALID_ARGUMENT, "input %d base is NULL", k);
     for (int o = 0; o < n_out; ++o) if (!outputs[o].base) return fail(TRS_ERR_INVALID_ARGUMENT, "output %d base is NULL", o);
 
+    // A dimension of 2^31 or more elements is cut into (outer x inner) with a power-of-two inner
+    // extent, so that every extent fits the 32-bit index arithmetic of the kernels.
+    for (size_t j = 0; j < dims.size(); ++j) {
+        if (dims[j].size < (1ll << 31)) continue;
+        long long inner = 1ll << 30;
+        while (inner > 1 && dims[j].size % inner != 0) inner >>= 1;
+        if (dims[j].size / inner >= (1ll << 31))
+            return fail(TRS_ERR_UNSUPPORTED, "a dimension of %lld elements cannot be split for 32-bit indexing", dims[j].size);
+        Dim outer = dims[j];
+        outer.size = dims[j].size / inner;
+        for (int k = 0; k < n_in; ++k) outer.in_s[k] = dims[j].in_s[k] * inner;
+        for (int o = 0; o < n_out; ++o) outer.out_s[o] = dims[j].out_s[o] * inner;
+        dims[j].size = inner;
+        dims.insert(dims.begin() + j, outer);      // the outer part precedes the inner part, like a leading axis
+        ++j;
+    }
     if (dims.empty()) { Dim d{}; d.size = 1; dims.push_back(d); }
     // Innermost first, by the first output's stride.
     std::stable_sort(dims.begin(), dims.end(), [](const Dim& x, const Dim& y) { return x.out_s[0] < y.out_s[0]; });
@@ -123,16 +139,13 @@ int32_t pw_make_plan(const trs_program* prog, const trs_operand* inputs, const t
         bool ok = true;
         for (int k = 0; k < n_in && ok; ++k) ok = dims[j].in_s[k] == prev.in_s[k] * prev.size;
         for (int o = 0; o < n_out && ok; ++o) ok = dims[j].out_s[o] == prev.out_s[o] * prev.size;
+        ok = ok && prev.size * dims[j].size < (1ll << 31);
         if (ok) prev.size *= dims[j].size;
         else merged.push_back(dims[j]);
     }
     const int nd = (int)merged.size();
     plan->ndim = nd;
-    for (const Dim& d : merged)
-        if (d.size >= (1ll << 31)) {
-            // Split an oversized run in two so that every size fits the 32-bit fast division.
-            return fail(TRS_ERR_UNSUPPORTED, "a collapsed dimension of %lld elements exceeds 2^31-1", d.size);
-        }
+    if (nd > TRS_MAX_RANK) return fail(TRS_ERR_UNSUPPORTED, "operand layout needs %d index dimensions (limit %d)", nd, TRS_MAX_RANK);
 
     PwParams& p = plan->params;
     std::memset(&p, 0, sizeof p);

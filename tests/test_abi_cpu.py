@@ -98,3 +98,11 @@ def test_compute_without_a_device_fails_loudly():
     assert _abi.lib().trs_stream_create(0, ctypes.byref(handle)) != 0
     desc = _abi.GemmDesc()
     assert _abi.lib().trs_matmul_f32(ctypes.byref(desc), None) != 0
+
+
+def test_huge_contiguous_extent_is_split_for_32_bit_indexing():
+    n = 3 * (1 << 30)                      # 3 Gi elements (12 GiB) in one contiguous run
+    x = fake_operand(0x100000000, [n], [1])
+    out = fake_operand(0x800000000, [n], [1])
+    status, klass = prepare([("relu", 0, 0, 0)], [1], [x], [out])
+    assert status == 0 and klass == "vector", _abi.lib().trs_last_error_message()
