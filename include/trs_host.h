@@ -40,6 +40,9 @@ int32_t trsh_from_host(const float* data, int32_t rank, const int64_t* shape, in
 int32_t trsh_from_pinned_host(const float* data, int32_t rank, const int64_t* shape, int32_t device, trsh_tensor* out);
 int32_t trsh_full(int32_t rank, const int64_t* shape, float value, int32_t device, trsh_tensor* out);
 int32_t trsh_to_host(trsh_tensor t, float* out);          /* logical row-major order, numel floats */
+/* Read-back into page-locked memory that does not wait: the copy runs on a second stream behind the
+ * kernels that produce `t`, overlapping later uploads and kernels; `out` is valid after trsh_sync. */
+int32_t trsh_to_pinned_host_async(trsh_tensor t, float* out);
 int32_t trsh_item(trsh_tensor t, float* out);
 int32_t trsh_release(trsh_tensor t);
 

@@ -59,6 +59,7 @@ int32_t trsh_full(int32_t rank, const int64_t* shape, float value, int32_t devic
     return guarded([&] { *out = wrap(full(shape_of(rank, shape), value, device)); });
 }
 int32_t trsh_to_host(trsh_tensor t, float* out) { return guarded([&] { to_host(*get(t), out); }); }
+int32_t trsh_to_pinned_host_async(trsh_tensor t, float* out) { return guarded([&] { to_host_async(get(t), out); }); }
 int32_t trsh_item(trsh_tensor t, float* out) { return guarded([&] { *out = item(*get(t)); }); }
 int32_t trsh_release(trsh_tensor t) {
     return guarded([&] { delete t; });

@@ -44,7 +44,46 @@ Storage::~Storage() {
     if (ptr) trs_free(device, ptr);
 }
 
-void sync(int device) { check_cuda(trs_stream_sync(stream_for(device)), "stream sync"); }
+namespace {
+// Read-backs in flight on the per-device egress stream: the tensor is kept alive (so its block is
+// not handed out again) until the device has finished copying it.
+struct Egress {
+    trs_stream stream = nullptr;
+    trs_event ready = nullptr;
+    std::vector<TensorP> in_flight;
+};
+std::map<int, Egress> g_egress;
+}  // namespace
+
+void sync(int device) {
+    check_cuda(trs_stream_sync(stream_for(device)), "stream sync");
+    auto it = g_egress.find(device);
+    if (it != g_egress.end() && it->second.stream) {
+        check_cuda(trs_stream_sync(it->second.stream), "egress stream sync");
+        it->second.in_flight.clear();
+    }
+}
+
+// Device-to-host copy into page-locked memory that returns at once: it runs on a second stream
+// (behind an event on the compute stream), so it overlaps later uploads and kernels.  The data
+// is valid after sync(device).
+void to_host_async(const TensorP& t, float* out) {
+    if (t->numel == 0) return;
+    const int device = t->device();
+    TensorP src = t;
+    if (!layout_is_contiguous(t->v.shape, t->v.strides))
+        src = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, contiguous_strides(t->v.shape), device);
+    materialize(src->v.st);
+    Egress& e = g_egress[device];
+    if (!e.stream) {
+        check_cuda(trs_stream_create(device, &e.stream), "creating the egress stream");
+        check_cuda(trs_event_create(&e.ready), "creating the egress event");
+    }
+    check_cuda(trs_event_record(e.ready, stream_for(device)), "egress event");
+    check_cuda(trs_stream_wait_event(e.stream, e.ready), "egress wait");
+    check_cuda(trs_memcpy_d2h(out, src->v.st->ptr + src->v.offset, (size_t)t->numel * 4, e.stream), "device to host copy");
+    e.in_flight.push_back(src);
+}
 
 static std::shared_ptr<Storage> alloc_storage(i64 count, int device) {
     auto st = std::make_shared<Storage>();

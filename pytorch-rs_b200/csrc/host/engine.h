@@ -120,6 +120,7 @@ void check_cuda(int32_t status, const char* what);
 TensorP from_host(const float* data, const Shape& shape, int device, bool pinned = false);
 TensorP full(const Shape& shape, float value, int device);
 void to_host(const Tensor& t, float* out);                 // logical row-major order
+void to_host_async(const std::shared_ptr<Tensor>& t, float* out);   // pinned destination; valid after sync(device)
 float item(const Tensor& t);
 void materialize(const std::shared_ptr<Storage>& st);
 void sync(int device);

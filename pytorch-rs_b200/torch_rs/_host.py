@@ -21,6 +21,7 @@ _PROTOTYPES = {
     "trsh_from_pinned_host": [ctypes.c_void_p, ctypes.c_int32, I64P, ctypes.c_int32, HP],
     "trsh_full": [ctypes.c_int32, I64P, ctypes.c_float, ctypes.c_int32, HP],
     "trsh_to_host": [H, ctypes.c_void_p],
+    "trsh_to_pinned_host_async": [H, ctypes.c_void_p],
     "trsh_item": [H, F32P],
     "trsh_release": [H],
     "trsh_rank": [H, I32P],

@@ -170,11 +170,19 @@ class Tensor:
         _host.check(_host.lib().trsh_to_host(self._h, out.ctypes.data))
         return out.reshape(shape)
 
-    def copy_to_host(self, out):
-        """Write the values in logical order into a caller-provided float32 array (e.g. pinned memory)."""
+    def copy_to_host(self, out, non_blocking=False):
+        """Write the values in logical order into a caller-provided float32 array.  With
+        `non_blocking=True` and a page-locked array (`torch_rs.pinned_empty`) the call returns at once
+        and the copy overlaps later uploads and kernels; the data is valid after `torch_rs.synchronize`."""
         if out.dtype != np.float32 or not out.flags.c_contiguous or out.size != self.numel():
             raise ValueError("copy_to_host needs a C-contiguous float32 array with numel elements")
-        _host.check(_host.lib().trsh_to_host(self._h, out.ctypes.data))
+        if non_blocking:
+            from . import _device
+            if not _device.is_pinned(out):
+                raise ValueError("non_blocking copy_to_host needs an array from torch_rs.pinned_empty")
+            _host.check(_host.lib().trsh_to_pinned_host_async(self._h, out.ctypes.data))
+        else:
+            _host.check(_host.lib().trsh_to_host(self._h, out.ctypes.data))
         return out
 
     def cpu(self):

@@ -41,13 +41,19 @@ def test_transposed_view_broadcast_exp_chain(rows, cols):
     xs = RefTensor.from_numpy(rnd(0, rows, cols))
     b = RefTensor.from_numpy((0.1 * rnd(1, rows)).astype(np.float32))
     xt = xs.mT
-    expected = (2.0 * (xt + b).relu()).exp() - xt
+    exp_term = (2.0 * (xt + b).relu()).exp()
+    expected = exp_term - xt
     if rows > 1 and cols > 1:
         assert expected.strides == xt.strides      # tests/test_transpose.py:244-259 in the reference
     prog = [("add", 0, 1, 0), ("relu", 2, 0, 0), ("const", 0, 0, 2.0), ("mul", 3, 4, 0), ("exp", 5, 0, 0), ("sub", 6, 0, 0)]
-    (got,) = run_pointwise(prog, [7], [xt, b], [(expected.shape, expected.strides)])
-    ulp = ref.ulp_distance(got, expected.storage)
-    assert ulp.max() <= 2, f"max ulp {ulp.max()}"
+    layout = (expected.shape, expected.strides)
+    got_e, got = run_pointwise(prog, [6, 7], [xt, b], [layout, layout])
+    # exp itself: at most 2 ulp from libm; the subtraction is exact arithmetic on that value
+    assert ref.ulp_distance(got_e, exp_term.storage).max() <= 2
+    same = got_e.view(np.uint32) == exp_term.storage.view(np.uint32)
+    assert np.array_equal(got[same].view(np.uint32), expected.storage[same].view(np.uint32))
+    assert np.all(np.abs(got.astype(np.float64) - expected.storage) <=
+                  2 * np.spacing(np.abs(exp_term.storage)) + np.spacing(np.abs(expected.storage)))
 
 
 @pytest.mark.parametrize("rows,cols", [(100, 70), (64, 64), (257, 33), (8, 8), (1000, 24)])
