@@ -90,7 +90,7 @@ class RefTensor:
     # -- construction -----------------------------------------------------
     @classmethod
     def from_numpy(cls, array):
-        array = np.ascontiguousarray(array, dtype=np.float32)
+        array = np.asarray(array, dtype=np.float32, order="C")     # keeps rank 0
         return cls(array.reshape(-1), array.shape)
 
     @property

@@ -96,6 +96,20 @@ std::vector<TensorP> apply(const GradFn& fn, const TensorP& g, int device) {
         case GK::Relu:       // src/tensor.rs:3161-3176
             if (wants(0)) out[0] = contiguous_result(TRS_OP_RELU_VJP, {fn.saved[0], g->v}, fn.out_shape, device);
             break;
+        case GK::Sin:        // upstream * cos(input) (src/tensor.rs:3178-3185)
+            if (wants(0)) {
+                TensorP c = contiguous_result(TRS_OP_COS, {fn.saved[0]}, fn.out_shape, device);
+                out[0] = contiguous_result(TRS_OP_MUL, {g->v, c->v}, fn.out_shape, device);
+            }
+            break;
+        case GK::Sqrt:       // upstream / (2.0 * sqrt(input)) (src/tensor.rs:4416-4419)
+            if (wants(0)) {
+                TensorP r = contiguous_result(TRS_OP_SQRT, {fn.saved[0]}, fn.out_shape, device);
+                TensorP two = pointwise_node(TRS_OP_CONST, 2.0f, {}, fn.out_shape, contiguous_strides(fn.out_shape), device);
+                TensorP d = contiguous_result(TRS_OP_MUL, {two->v, r->v}, fn.out_shape, device);
+                out[0] = contiguous_result(TRS_OP_DIV, {g->v, d->v}, fn.out_shape, device);
+            }
+            break;
         case GK::Exp:        // d exp(x) = g * exp(x), with exp(x) the saved output
             if (wants(0)) out[0] = contiguous_result(TRS_OP_MUL, {g->v, fn.saved[0]}, fn.out_shape, device);
             break;

@@ -15,6 +15,8 @@ enum class GK {
     Permute,      // Permute/TransposeBackward0   src/tensor.rs:3248-3298
     Index,        // SelectBackward0         src/tensor.rs:3237-3247
     Copy,         // clone / contiguous      src/tensor.rs:3236
+    Sin,          // SinBackward0            src/tensor.rs:3178-3185
+    Sqrt,         // SqrtBackward0           src/tensor.rs:3187-3202, 4416-4419
     // Edges the reference does not record on CPU; CUDA tensors gain them:
     Add,          // AddBackward0 (tensor + tensor)
     Sub,          // SubBackward0 (tensor - tensor)

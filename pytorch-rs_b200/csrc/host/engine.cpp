@@ -6,6 +6,8 @@
 // fusion IR of the C ABI and runs it as one kernel when a value is needed.
 #include "engine.h"
 
+#include "autograd.h"
+
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -239,7 +241,9 @@ float item(const Tensor& t) {
 
 TensorP contiguous(const TensorP& t) {
     if (layout_is_contiguous(t->v.shape, t->v.strides)) return t;
-    return pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, contiguous_strides(t->v.shape), t->device());
+    TensorP out = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, contiguous_strides(t->v.shape), t->device());
+    if (t->requires_grad() && grad_enabled()) record(out, GK::Copy, "CloneBackward0", {t.get()}, {}, false);
+    return out;
 }
 
 }  // namespace trsh

@@ -64,7 +64,11 @@ TensorP unary(const TensorP& t, int op) {
             case TRS_OP_RELU: record(out, GK::Relu, "ReluBackward0", {t.get()}, {t->v}, true); break;
             case TRS_OP_NEG: record(out, GK::Neg, "NegBackward0", {t.get()}, {}, false); break;
             case TRS_OP_EXP: record(out, GK::Exp, "ExpBackward0", {t.get()}, {out->v}, true); break;
-            default: break;    // sin / sqrt VJPs and reciprocal are outside the CUDA path's scope
+            case TRS_OP_SIN: record(out, GK::Sin, "SinBackward0", {t.get()}, {t->v}, true); break;
+            case TRS_OP_SQRT: record(out, GK::Sqrt, "SqrtBackward0", {t.get()}, {t->v}, true); break;
+            case TRS_OP_RECIP:   // src/tensor.rs:2348-2353
+                throw Error(ErrKind::InvalidArgument, "reciprocal(): autograd recording is not supported");
+            default: break;
         }
     }
     return out;

@@ -24,7 +24,7 @@ def tensor(data, *, dtype=None, device=None, requires_grad=False) -> Tensor:
     """`torch.tensor(data, device="cuda[:N]")`: one bulk host-to-device copy of any array-like
     (the reference ingests buffers at src/python.rs:10329-10403)."""
     index = _device_index(device)
-    array = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
+    array = np.asarray(data, dtype=np.float32, order="C")      # keeps rank 0 (ascontiguousarray would not)
     shape = (ctypes.c_int64 * max(array.ndim, 1))(*array.shape)
     out = ctypes.c_void_p()
     # Arrays that live in page-locked staging memory (torch_rs.pinned_empty) are copied without waiting.
@@ -88,6 +88,18 @@ def exp(input):
 
 def neg(input):
     return _tensor_arg(input, "neg").neg()
+
+
+def sin(input):
+    return _tensor_arg(input, "sin").sin()
+
+
+def sqrt(input):
+    return _tensor_arg(input, "sqrt").sqrt()
+
+
+def reciprocal(input):
+    return _tensor_arg(input, "reciprocal").reciprocal()
 
 
 def add(input, other):
