@@ -99,7 +99,8 @@ def test_empty_and_zero_inner():
     assert c.shape == (4, 3) and np.all(c == 0.0)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 32), (129, 257, 40), (300, 520, 100), (1024, 768, 2048), (64, 64, 4096)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 32), (129, 257, 40), (300, 520, 100), (1024, 768, 2048), (64, 64, 4096),
+                                   (1664, 3072, 256), (1700, 3000, 264)])   # 156 tiles on 148 SMs: the split-K tail
 def test_tensor_core_path_odd_shapes_and_k_tails(m, n, k):
     a, b = RefTensor.from_numpy(rnd(20, m, k)), RefTensor.from_numpy(rnd(21, k, n, scale=1 / np.sqrt(k)))
     c, _ = run(a, b, "tcgen05_3xtf32")
