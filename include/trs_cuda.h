@@ -81,7 +81,8 @@ typedef enum trs_op {
     TRS_OP_SQRT = 10,      /* src/tensor.rs:4402-4414 */
     TRS_OP_SIN = 11,       /* src/tensor.rs:2388 */
     TRS_OP_COS = 12,       /* used by the sin VJP, src/tensor.rs:3178-3185 */
-    TRS_OP_COPY = 13       /* identity; materialises a view (src/tensor.rs:1805-1838) */
+    TRS_OP_COPY = 13,      /* identity; materialises a view (src/tensor.rs:1805-1838) */
+    TRS_OP_NE = 14         /* a != b ? 1.0 : 0.0 (IEEE: NaN differs from everything, -0 equals +0); Tensor::eq src/tensor.rs:286-293 */
 } trs_op;
 
 typedef struct trs_instr {

@@ -28,7 +28,8 @@ enum {
     TRSH_MATRIX_TRANSPOSE_REQUIRES_MATRIX = 10, TRSH_STRIDE_OVERFLOW = 11, TRSH_ELEMENT_COUNT_OVERFLOW = 12,
     TRSH_ALLOCATION_FAILED = 13, TRSH_BACKWARD_REQUIRES_SCALAR = 14, TRSH_DOES_NOT_REQUIRE_GRAD = 15,
     TRSH_BACKWARD_GRAPH_FREED = 16, TRSH_INVALID_SCALAR_INDEX = 17, TRSH_DEVICE_MISMATCH = 18, TRSH_DEVICE = 19,
-    TRSH_INVALID_ARGUMENT = 20, TRSH_SHAPE_DATA_MISMATCH = 21
+    TRSH_INVALID_ARGUMENT = 20, TRSH_SHAPE_DATA_MISMATCH = 21, TRSH_RESHAPE_INVALID = 22,
+    TRSH_VIEW_INCOMPATIBLE_LAYOUT = 23
 };
 
 const char* trsh_last_error(void);
@@ -63,6 +64,11 @@ int32_t trsh_reverse_dims(trsh_tensor t, trsh_tensor* out);        /* .T  */
 int32_t trsh_select0(trsh_tensor t, int64_t index, trsh_tensor* out);
 int32_t trsh_detach(trsh_tensor t, trsh_tensor* out);
 int32_t trsh_contiguous(trsh_tensor t, trsh_tensor* out);
+/* materialising layout ops: try_clone (src/tensor.rs:1517-1575), reshape / view (2032-2189; `view_only`
+ * fails instead of copying), PartialEq (286-293) */
+int32_t trsh_clone(trsh_tensor t, trsh_tensor* out);
+int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out);
+int32_t trsh_equal(trsh_tensor a, trsh_tensor b, int32_t* result);
 
 /* pointwise (src/tensor.rs:2197-2410); `op` is a trs_op from trs_cuda.h */
 int32_t trsh_unary(trsh_tensor t, int32_t op, trsh_tensor* out);

@@ -664,6 +664,44 @@ void ref_accumulate(float* grad, const float* contribution, i64 n) {
     for (i64 i = 0; i < n; ++i) grad[i] += contribution[i];
 }
 
+// Strides of a metadata-only reshape, or status 7 when the layout cannot be viewed that way
+// (compute_reshape_view_strides, tensor.rs:3996-4055; empty tensors 2152-2164 are not covered here).
+int ref_reshape_view_strides(int rank, const i64* shape, const i64* strides, int new_rank, const i64* new_shape,
+                             i64* out_strides) {
+    if (rank == 0) {
+        std::vector<i64> ns(new_shape, new_shape + new_rank), o;
+        if (int s = contiguous_strides(ns, o)) return s;
+        std::copy(o.begin(), o.end(), out_strides);
+        return OK;
+    }
+    int view_d = new_rank;
+    i64 chunk_base = strides[rank - 1], tensor_n = 1, view_n = 1;
+    for (int d = rank - 1; d >= 0; --d) {
+        tensor_n *= shape[d];
+        bool ends = d == 0 || (shape[d - 1] != 1 && strides[d - 1] != tensor_n * chunk_base);
+        if (!ends) continue;
+        while (view_d > 0 && (view_n < tensor_n || new_shape[view_d - 1] == 1)) {
+            --view_d;
+            out_strides[view_d] = view_n * chunk_base;
+            view_n *= new_shape[view_d];
+        }
+        if (view_n != tensor_n) return 7;
+        if (d > 0) { chunk_base = strides[d - 1]; tensor_n = 1; view_n = 1; }
+    }
+    return view_d == 0 ? OK : 7;
+}
+
+// Strides of clone() with the preserve format (tensor.rs:1535-1575): dense layouts keep their
+// strides, others are packed in the same dimension order.
+int ref_clone_strides(int rank, const i64* shape, const i64* strides, i64* out_strides) {
+    View v = make_view(nullptr, 0, rank, shape, strides);
+    std::vector<i64> o;
+    if (v.elements() == 0 || is_non_overlapping_and_dense(v.shape, v.strides, v.elements())) o = v.strides;
+    else if (int s = elementwise_output_strides(v.shape, {Layout{&v.shape, &v.strides}}, o)) return s;
+    std::copy(o.begin(), o.end(), out_strides);
+    return OK;
+}
+
 float ref_relu_value(float v) { return relu_value(v); }
 float ref_relu_backward_value(float x, float g) { return relu_backward_value(x, g); }
 

@@ -123,6 +123,40 @@ class RefTensor:
             index += self.shape[0]
         return RefTensor(self.storage, self.shape[1:], self.strides[1:], self.offset + index * self.strides[0])
 
+    def reshape(self, shape):
+        """View when the strides allow it, else a packed copy (tensor.rs:2032-2148)."""
+        shape = list(shape)
+        if -1 in shape:
+            known = 1
+            for d in shape:
+                if d != -1:
+                    known *= d
+            shape[shape.index(-1)] = self.numel // known
+        out = _i64([0] * len(shape))
+        status = lib().ref_reshape_view_strides(len(self.shape), _i64(self.shape), _i64(self.strides), len(shape),
+                                                _i64(shape), out)
+        if status == 0:
+            return RefTensor(self.storage, shape, list(out)[:len(shape)], self.offset)
+        if status != 7:
+            raise RefError(status)
+        return RefTensor(self.logical().reshape(-1), shape)
+
+    def view_strides(self, shape):
+        out = _i64([0] * len(shape))
+        status = lib().ref_reshape_view_strides(len(self.shape), _i64(self.shape), _i64(self.strides), len(shape),
+                                                _i64(list(shape)), out)
+        return list(out)[:len(shape)] if status == 0 else None
+
+    def clone(self):
+        out = _i64([0] * len(self.shape))
+        _check(lib().ref_clone_strides(len(self.shape), _i64(self.shape), _i64(self.strides), out))
+        strides = list(out)[:len(self.shape)]
+        packed = np.zeros(self.numel, dtype=np.float32)
+        if self.numel:
+            dst = np.lib.stride_tricks.as_strided(packed, self.shape, [4 * s for s in strides])
+            dst[...] = self.logical()
+        return RefTensor(packed, self.shape, strides)
+
     # -- egress -----------------------------------------------------------------
     def logical(self):
         """Values in logical row-major order as an ndarray of ``shape``."""

@@ -93,6 +93,12 @@ std::vector<TensorP> apply(const GradFn& fn, const TensorP& g, int device) {
         case GK::Copy:
             if (wants(0)) out[0] = g;
             break;
+        case GK::Reshape:    // the gradient keeps its flat logical order and takes the input's shape
+            if (wants(0)) {
+                TensorP c = contiguous(g);
+                out[0] = make_tensor(View{c->v.st, fn.in[0].shape, contiguous_strides(fn.in[0].shape), c->v.offset});
+            }
+            break;
         case GK::Relu:       // src/tensor.rs:3161-3176
             if (wants(0)) out[0] = contiguous_result(TRS_OP_RELU_VJP, {fn.saved[0], g->v}, fn.out_shape, device);
             break;

@@ -15,6 +15,7 @@ enum class GK {
     Permute,      // Permute/TransposeBackward0   src/tensor.rs:3248-3298
     Index,        // SelectBackward0         src/tensor.rs:3237-3247
     Copy,         // clone / contiguous      src/tensor.rs:3236
+    Reshape,      // ViewBackward0: same flat logical order, other shape   src/tensor.rs:2127-2189, 3236
     Sin,          // SinBackward0            src/tensor.rs:3178-3185
     Sqrt,         // SqrtBackward0           src/tensor.rs:3187-3202, 4416-4419
     // Edges the reference does not record on CPU; CUDA tensors gain them:

@@ -111,6 +111,12 @@ int32_t trsh_select0(trsh_tensor t, int64_t index, trsh_tensor* out) { return gu
 int32_t trsh_detach(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out = wrap(detach(get(t))); }); }
 int32_t trsh_contiguous(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out = wrap(contiguous(get(t))); }); }
 
+int32_t trsh_clone(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out = wrap(clone(get(t))); }); }
+int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out) {
+    return guarded([&] { *out = wrap(reshape(get(t), std::vector<i64>(shape, shape + n), view_only != 0)); });
+}
+int32_t trsh_equal(trsh_tensor a, trsh_tensor b, int32_t* result) { return guarded([&] { *result = equal(get(a), get(b)); }); }
+
 int32_t trsh_unary(trsh_tensor t, int32_t op, trsh_tensor* out) { return guarded([&] { *out = wrap(unary(get(t), op)); }); }
 int32_t trsh_scalar(trsh_tensor t, int32_t op, float scalar, int32_t reflected, trsh_tensor* out) {
     return guarded([&] { *out = wrap(scalar_op(get(t), op, scalar, reflected != 0)); });

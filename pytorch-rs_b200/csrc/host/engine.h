@@ -43,6 +43,8 @@ enum class ErrKind : int {
     Device = 19,            // a libtrs_cuda call failed (no device, CUDA error, ...)
     InvalidArgument = 20,
     ShapeDataMismatch = 21,
+    ReshapeInvalid = 22,
+    ViewIncompatibleLayout = 23,
 };
 
 struct Error : std::runtime_error {
@@ -108,6 +110,8 @@ bool layout_is_contiguous(const Shape& shape, const Shape& strides);
 bool is_non_overlapping_and_dense(const Shape& shape, const Shape& strides);
 Shape unary_output_strides(const Shape& shape, const Shape& strides);
 Shape scalar_output_strides(const Shape& shape, const Shape& strides);
+bool reshape_view_strides(const Shape& shape, const Shape& strides, const Shape& new_shape, Shape* out);
+Shape clone_strides(const Shape& shape, const Shape& strides);
 void binary_plan(const Shape& lshape, const Shape& lstrides, const Shape& rshape, const Shape& rstrides,
                  Shape* shape, Shape* strides);
 
@@ -132,6 +136,9 @@ TensorP reverse_dims(const TensorP& t);
 TensorP select0(const TensorP& t, i64 index);
 TensorP detach(const TensorP& t);
 TensorP contiguous(const TensorP& t);
+TensorP clone(const TensorP& t);
+TensorP reshape(const TensorP& t, const std::vector<i64>& requested, bool view_only);
+bool equal(const TensorP& a, const TensorP& b);
 
 TensorP unary(const TensorP& t, int op);                   // relu, exp, neg, sin, sqrt, reciprocal
 TensorP scalar_op(const TensorP& t, int op, float s, bool reflected);

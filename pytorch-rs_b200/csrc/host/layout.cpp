@@ -173,6 +173,34 @@ Shape scalar_output_strides(const Shape& shape, const Shape& strides) {
     return sorted_output_strides(shape, {Operand{&shape, &strides}});
 }
 
+// compute_reshape_view_strides (src/tensor.rs:3996-4055): strides that let `new_shape` alias the same
+// elements, or false when some new dimension would straddle two runs of the old layout.
+bool reshape_view_strides(const Shape& shape, const Shape& strides, const Shape& new_shape, Shape* out) {
+    if (shape.empty()) { *out = contiguous_strides(new_shape); return true; }
+    out->assign(new_shape.size(), 0);
+    size_t view_d = new_shape.size();
+    i64 chunk_base = strides.back(), tensor_n = 1, view_n = 1;
+    for (size_t d = shape.size(); d-- > 0;) {
+        tensor_n *= shape[d];
+        const bool ends = d == 0 || (shape[d - 1] != 1 && strides[d - 1] != tensor_n * chunk_base);
+        if (!ends) continue;
+        while (view_d > 0 && (view_n < tensor_n || new_shape[view_d - 1] == 1)) {
+            --view_d;
+            (*out)[view_d] = view_n * chunk_base;
+            view_n *= new_shape[view_d];
+        }
+        if (view_n != tensor_n) return false;
+        if (d > 0) { chunk_base = strides[d - 1]; tensor_n = 1; view_n = 1; }
+    }
+    return view_d == 0;
+}
+
+// clone() with the preserve format (src/tensor.rs:1555-1565)
+Shape clone_strides(const Shape& shape, const Shape& strides) {
+    if (is_non_overlapping_and_dense(shape, strides)) return strides;
+    return sorted_output_strides(shape, {Operand{&shape, &strides}});
+}
+
 static std::string shape_text(const Shape& s) {
     std::string t = "[";
     for (size_t i = 0; i < s.size(); ++i) t += (i ? ", " : "") + std::to_string(s[i]);

@@ -7,7 +7,7 @@
 
 namespace trsh {
 
-static std::string shape_text(const Shape& s) {
+static std::string shape_text(const std::vector<i64>& s) {
     std::string t = "[";
     for (size_t i = 0; i < s.size(); ++i) t += (i ? ", " : "") + std::to_string(s[i]);
     return t + "]";
@@ -164,6 +164,86 @@ TensorP matmul(const TensorP& l, const TensorP& r) {
         record(out, GK::Matmul, shape.size() == 3 ? "BmmBackward0" : "MmBackward0", {l.get(), r.get()},
                {r->meta ? l->v : View{}, l->meta ? r->v : View{}}, true);
     return out;
+}
+
+// try_clone (src/tensor.rs:1517-1575): an independent copy; dense layouts keep their strides,
+// other views are packed in the same dimension order; offset 0.
+TensorP clone(const TensorP& t) {
+    const Shape strides = clone_strides(t->v.shape, t->v.strides);
+    TensorP out = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, strides, t->device());
+    if (t->requires_grad() && grad_enabled()) record(out, GK::Copy, "CloneBackward0", {t.get()}, {}, false);
+    return out;
+}
+
+// reshape / view (src/tensor.rs:2032-2189): a metadata-only alias when the strides can express the
+// new shape, otherwise (reshape only) a packed copy.
+TensorP reshape(const TensorP& t, const std::vector<i64>& requested, bool view_only) {
+    // resolve_reshape_shape (src/tensor.rs:2057-2125)
+    int inferred = -1;
+    for (size_t i = 0; i < requested.size(); ++i) {
+        if (requested[i] == -1) {
+            if (inferred >= 0) throw Error(ErrKind::ReshapeInvalid, "only one dimension can be inferred");
+            inferred = (int)i;
+        } else if (requested[i] < 0) {
+            throw Error(ErrKind::ReshapeInvalid, "invalid shape dimension " + std::to_string(requested[i]) + " at index " +
+                                                     std::to_string(i) + " of shape " + shape_text(requested));
+        }
+    }
+    Shape resolved(requested.begin(), requested.end());
+    auto mismatch = [&]() {
+        return Error(ErrKind::ReshapeInvalid, "shape '" + shape_text(requested) + "' is invalid for input of size " + std::to_string(t->numel));
+    };
+    if (inferred >= 0) {
+        i64 known = 1;
+        for (size_t i = 0; i < requested.size(); ++i) if ((int)i != inferred) known *= requested[i];
+        if (known == 0) {
+            if (t->numel == 0)
+                throw Error(ErrKind::ReshapeInvalid, "cannot reshape tensor of 0 elements into shape " + shape_text(requested) +
+                                                         " because the unspecified dimension size -1 can be any value and is ambiguous");
+            throw mismatch();
+        }
+        if (t->numel % known != 0) throw mismatch();
+        resolved[inferred] = t->numel / known;
+    }
+    if (element_count(resolved) != t->numel) throw mismatch();
+
+    Shape strides;
+    bool viewable;
+    if (t->numel == 0) { viewable = true; strides = resolved == t->v.shape ? t->v.strides : contiguous_strides(resolved); }
+    else viewable = reshape_view_strides(t->v.shape, t->v.strides, resolved, &strides);
+    TensorP out;
+    if (viewable) {
+        out = make_tensor(View{t->v.st, resolved, strides, t->v.offset});
+        out->view_requires_grad = t->requires_grad();
+    } else {
+        if (view_only)
+            throw Error(ErrKind::ViewIncompatibleLayout, "view size is not compatible with input tensor's size and stride (at least one dimension "
+                                                         "spans across two contiguous subspaces). Use .reshape(...) instead.");
+        TensorP packed;
+        {
+            // the packing copy is not a tape node of its own: the reshape edge covers it
+            const bool was = grad_enabled();
+            if (was) set_grad_enabled(false);
+            packed = contiguous(t);
+            if (was) set_grad_enabled(true);
+        }
+        out = make_tensor(View{packed->v.st, resolved, contiguous_strides(resolved), 0});
+    }
+    if (t->requires_grad() && grad_enabled()) record(out, GK::Reshape, "ViewBackward0", {t.get()}, {}, false);
+    return out;
+}
+
+// Tensor equality (PartialEq, src/tensor.rs:286-293): same shape and every pair of logical values
+// compares equal under IEEE rules (NaN equals nothing, -0.0 equals +0.0).
+bool equal(const TensorP& a, const TensorP& b) {
+    if (a->v.shape != b->v.shape || a->device() != b->device()) return false;
+    if (a->numel == 0) return true;
+    const bool was = grad_enabled();
+    if (was) set_grad_enabled(false);
+    TensorP differing = pointwise_node(TRS_OP_NE, 0.f, {a->v, b->v}, a->v.shape, contiguous_strides(a->v.shape), a->device());
+    TensorP count = sum(differing);
+    if (was) set_grad_enabled(true);
+    return item(*count) == 0.0f;
 }
 
 // Tensor::sum (src/tensor.rs:2413-2431): all elements -> rank-0 tensor.

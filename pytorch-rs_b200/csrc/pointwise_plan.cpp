@@ -39,7 +39,7 @@ void magic_for(unsigned d, unsigned* magic, unsigned* shift) {
 bool arity_ok(int op, int* n_args) {
     switch (op) {
         case TRS_OP_CONST: *n_args = 0; return true;
-        case TRS_OP_ADD: case TRS_OP_SUB: case TRS_OP_MUL: case TRS_OP_DIV: case TRS_OP_RELU_VJP:
+        case TRS_OP_ADD: case TRS_OP_SUB: case TRS_OP_MUL: case TRS_OP_DIV: case TRS_OP_RELU_VJP: case TRS_OP_NE:
             *n_args = 2; return true;
         case TRS_OP_NEG: case TRS_OP_RELU: case TRS_OP_EXP: case TRS_OP_RECIP: case TRS_OP_SQRT:
         case TRS_OP_SIN: case TRS_OP_COS: case TRS_OP_COPY:
@@ -319,6 +319,7 @@ void emit_chain(std::ostringstream& s, const trs_program* prog) {
             case TRS_OP_SQRT: s << d << "trs_sqrt(" << a << ");\n"; break;
             case TRS_OP_SIN: s << d << "sinf(" << a << ");\n"; break;
             case TRS_OP_COS: s << d << "cosf(" << a << ");\n"; break;
+            case TRS_OP_NE: s << d << "((" << a << " != " << b << ") ? 1.0f : 0.0f);\n"; break;
             default: s << d << a << ";\n"; break;
         }
     }

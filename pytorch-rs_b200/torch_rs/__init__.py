@@ -72,6 +72,22 @@ def ones(*size, dtype=None, device=None, requires_grad=False) -> Tensor:
     return full(_sizes(size), 1.0, device=device, requires_grad=requires_grad)
 
 
+def eye(n, m=None, *, dtype=None, device=None, requires_grad=False) -> Tensor:
+    return tensor(np.eye(n, n if m is None else m, dtype=np.float32), device=device, requires_grad=requires_grad)
+
+
+def equal(input, other) -> bool:
+    return _tensor_arg(input, "equal").equal(other)
+
+
+def reshape(input, shape):
+    return _tensor_arg(input, "reshape").reshape(*shape)
+
+
+def clone(input):
+    return _tensor_arg(input, "clone").clone()
+
+
 def _tensor_arg(value, name):
     if not isinstance(value, Tensor):
         raise TypeError(f"{name}(): argument 'input' (position 1) must be Tensor, not {type(value).__name__}")

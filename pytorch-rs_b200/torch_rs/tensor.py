@@ -251,6 +251,42 @@ class Tensor:
     def contiguous(self):
         return self._view(_host.lib().trsh_contiguous)
 
+    def clone(self):
+        return self._view(_host.lib().trsh_clone)
+
+    def _reshape(self, shape, view_only):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+            shape = tuple(shape[0])
+        arr = (ctypes.c_int64 * max(len(shape), 1))(*shape)
+        return self._view(_host.lib().trsh_reshape, len(shape), arr, int(view_only))
+
+    def reshape(self, *shape):
+        return self._reshape(shape, False)
+
+    def view(self, *shape):
+        return self._reshape(shape, True)
+
+    def flatten(self, start_dim=0, end_dim=-1):
+        shape = list(self.shape)
+        rank = max(len(shape), 1)
+        start, end = start_dim % rank, end_dim % rank
+        if start > end:
+            raise RuntimeError("flatten() has invalid args: start_dim cannot come after end_dim")
+        if not shape:
+            return self.reshape(1)
+        merged = 1
+        for d in shape[start:end + 1]:
+            merged *= d
+        return self.reshape(*shape[:start], merged, *shape[end + 1:])
+
+    def ravel(self):
+        return self.contiguous().reshape(-1)
+
+    def equal(self, other):
+        r = ctypes.c_int32()
+        _host.check(_host.lib().trsh_equal(self._h, other._h, ctypes.byref(r)))
+        return bool(r.value)
+
     # ---- pointwise ----------------------------------------------------------------------------
     def _unary(self, name):
         return self._view(_host.lib().trsh_unary, OPS[name])
