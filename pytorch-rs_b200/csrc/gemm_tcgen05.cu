@@ -28,8 +28,9 @@ namespace trs {
 namespace {
 
 constexpr int BM = 128, BN = 256;
-constexpr int BK = 16;                                // floats per pipeline stage along K (16 -> 64-byte swizzle rows, 32 -> 128-byte)
-constexpr int STAGES = BK == 16 ? 4 : 2;
+constexpr int BK = 16;                                // floats per pipeline stage along K: 8 / 16 / 32 -> 32- / 64- / 128-byte swizzled rows.
+                                                      // Measured at 4096^3: 16 x 4 stages 256 TFLOP/s, 32 x 2 stages 223, 8 x 8 stages 155.
+constexpr int STAGES = BK == 8 ? 8 : (BK == 16 ? 4 : 2);
 constexpr int ROW_BYTES = BK * 4;
 constexpr int A_TILE_BYTES = BM * ROW_BYTES;
 constexpr int B_TILE_BYTES = BN * ROW_BYTES;
@@ -75,7 +76,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
     d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;       // stride between 8-row groups
     d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
-    d |= (uint64_t)(ROW_BYTES == 128 ? 2 : 4) << 61;
+    d |= (uint64_t)(ROW_BYTES == 128 ? 2 : (ROW_BYTES == 64 ? 4 : 6)) << 61;
     return d;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -471,7 +472,7 @@ int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long
     cuuint64_t dims[3] = {(cuuint64_t)k_pad, (cuuint64_t)rows, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)k_pad * 4, (cuuint64_t)rows * (cuuint64_t)k_pad * 4};
     cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-    const CUtensorMapSwizzle swizzle = ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUtensorMapSwizzle swizzle = ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (ROW_BYTES == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
