@@ -351,6 +351,7 @@ def run_ours(args, rank, world, local_rank):
 
 WORKLOADS = {
     "c1": "relu(x + y), x,y f32 [4096,4096] contiguous ~U(-1,1); 4 rotating operand sets defeat L2",
+    "t1": "x.mT + y, x,y f32 [8192,8192] ~N(0,1): operand layouts disagree, staged through shared-memory tiles",
     "c3": "matmul(A, B), f32 [4096,4096]^2 ~N(0,1/64), precision highest",
     "c4": "relu(X @ W.mT + bias), X,W f32 [64,1024,1024], bias [1024]; batches sharded over ranks",
     "c5": "2-layer MLP forward+backward, X f32 [65536,4096], W1 [4096,4096], W2 [4096,1024], b1 [4096]; "
@@ -386,6 +387,15 @@ def run_side_workload(args, rank, world, local_rank):
             xa, ya = sets[it[0] % 4]
             it[0] += 1
             held[0] = torch.relu(xa + ya).materialize()
+        work, unit, metric, bound, peak = 12 * n * n * world, "GB/s", "fused pointwise GB/s", "hbm", hbm_peak
+        scale, scaling = 1e9, "weak"
+    elif name == "t1":
+        n = 8192
+        xt = torch.tensor(rng.standard_normal((n, n)).astype(np.float32), device=dev)
+        yt = torch.tensor(rng.standard_normal((n, n)).astype(np.float32), device=dev)
+
+        def step():
+            held[0] = (xt.mT + yt).materialize()
         work, unit, metric, bound, peak = 12 * n * n * world, "GB/s", "fused pointwise GB/s", "hbm", hbm_peak
         scale, scaling = 1e9, "weak"
     elif name == "c3":
@@ -458,7 +468,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "t1", "c3", "c4", "c5"],
                     help="c2 (default) is the headline fused chain; the others are BASELINE's remaining configs")
     ap.add_argument("--no-extra", action="store_true", help="skip the relu(x+y) and matmul side figures")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -283,3 +283,34 @@ def test_pinned_upload_and_non_blocking_read_back():
         out.copy_to_host(np.empty((96, 64), dtype=np.float32), non_blocking=True)
     torch.pinned_free(staging)
     torch.pinned_free(result)
+
+
+def test_concurrent_backward_passes_from_two_threads():
+    # The reference runs whole backward passes under one lock and tests it with two racing threads
+    # (tests/autograd.rs:128-173); here two Python threads share a leaf and each runs 20 backward passes.
+    import threading
+    x = torch.tensor(np.array([-2.0, 0.5, 3.0], dtype=np.float32), device=DEV, requires_grad=True)
+    errors = []
+
+    def worker():
+        try:
+            for _ in range(20):
+                (x * x).sum().backward()
+        except Exception as exc:            # pragma: no cover - reported below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker) for _ in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+    assert x.grad.tolist() == [-160.0, 40.0, 240.0]        # 40 accumulated passes of 2x
+
+
+def test_refused_allocation_is_reported_like_the_reference():
+    # AllocationFailed{elements} (src/tensor_error.rs): a request the device cannot satisfy is an error
+    # message, not a crash, and the engine keeps working afterwards.
+    with pytest.raises(RuntimeError, match=r"failed to allocate storage for 1099511627776 elements"):
+        torch.zeros(1 << 20, 1 << 20, device=DEV)
+    assert (torch.ones(4, device=DEV) + 1.0).tolist() == [2.0, 2.0, 2.0, 2.0]
