@@ -69,6 +69,8 @@ int32_t trsh_contiguous(trsh_tensor t, trsh_tensor* out);
 int32_t trsh_clone(trsh_tensor t, trsh_tensor* out);
 int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out);
 int32_t trsh_equal(trsh_tensor a, trsh_tensor b, int32_t* result);
+/* squeeze() (all != 0) / squeeze(dim): metadata-only (src/tensor.rs:1305-1336) */
+int32_t trsh_squeeze(trsh_tensor t, int32_t all, int64_t dimension, trsh_tensor* out);
 
 /* pointwise (src/tensor.rs:2197-2410); `op` is a trs_op from trs_cuda.h */
 int32_t trsh_unary(trsh_tensor t, int32_t op, trsh_tensor* out);

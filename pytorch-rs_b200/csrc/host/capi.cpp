@@ -115,6 +115,9 @@ int32_t trsh_clone(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out 
 int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out) {
     return guarded([&] { *out = wrap(reshape(get(t), std::vector<i64>(shape, shape + n), view_only != 0)); });
 }
+int32_t trsh_squeeze(trsh_tensor t, int32_t all, int64_t dimension, trsh_tensor* out) {
+    return guarded([&] { *out = wrap(squeeze(get(t), all ? INT64_MIN : dimension)); });
+}
 int32_t trsh_equal(trsh_tensor a, trsh_tensor b, int32_t* result) { return guarded([&] { *result = equal(get(a), get(b)); }); }
 
 int32_t trsh_unary(trsh_tensor t, int32_t op, trsh_tensor* out) { return guarded([&] { *out = wrap(unary(get(t), op)); }); }

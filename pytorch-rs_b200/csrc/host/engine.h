@@ -137,6 +137,7 @@ TensorP select0(const TensorP& t, i64 index);
 TensorP detach(const TensorP& t);
 TensorP contiguous(const TensorP& t);
 TensorP clone(const TensorP& t);
+TensorP squeeze(const TensorP& t, i64 dimension);    // INT64_MIN: every singleton dimension
 TensorP reshape(const TensorP& t, const std::vector<i64>& requested, bool view_only);
 bool equal(const TensorP& a, const TensorP& b);
 

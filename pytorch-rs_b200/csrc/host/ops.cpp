@@ -233,6 +233,32 @@ TensorP reshape(const TensorP& t, const std::vector<i64>& requested, bool view_o
     return out;
 }
 
+// squeeze() / squeeze(dim) (src/tensor.rs:1305-1336): drop singleton dimensions, sharing storage; a
+// chosen dimension whose size is not 1 gives an unchanged alias.  `dimension` == INT64_MIN means all.
+TensorP squeeze(const TensorP& t, i64 dimension) {
+    const size_t rank = t->v.shape.size();
+    i64 axis = -1;
+    if (dimension != INT64_MIN) {
+        const i64 r = (i64)std::max<size_t>(rank, 1);
+        if (dimension < -r || dimension >= r)
+            throw Error(ErrKind::DimensionOutOfRange, "Dimension out of range (expected to be in range of [-" + std::to_string(r) + ", " +
+                                                          std::to_string(r - 1) + "], but got " + std::to_string(dimension) + ")");
+        axis = rank == 0 ? 0 : (dimension < 0 ? dimension + r : dimension);
+    }
+    View v{t->v.st, {}, {}, t->v.offset};
+    for (size_t a = 0; a < rank; ++a) {
+        const bool drop = t->v.shape[a] == 1 && (dimension == INT64_MIN || (i64)a == axis);
+        if (drop) continue;
+        v.shape.push_back(t->v.shape[a]);
+        v.strides.push_back(t->v.strides[a]);
+    }
+    TensorP out = make_tensor(std::move(v));
+    out->view_requires_grad = t->requires_grad();
+    if (t->requires_grad() && grad_enabled())
+        record(out, GK::Reshape, dimension == INT64_MIN ? "SqueezeBackward0" : "SqueezeBackward1", {t.get()}, {}, false);
+    return out;
+}
+
 // Tensor equality (PartialEq, src/tensor.rs:286-293): same shape and every pair of logical values
 // compares equal under IEEE rules (NaN equals nothing, -0.0 equals +0.0).
 bool equal(const TensorP& a, const TensorP& b) {

@@ -40,6 +40,7 @@ _PROTOTYPES = {
     "trsh_clone": [H, HP],
     "trsh_reshape": [H, ctypes.c_int32, I64P, ctypes.c_int32, HP],
     "trsh_equal": [H, H, I32P],
+    "trsh_squeeze": [H, ctypes.c_int32, ctypes.c_int64, HP],
     "trsh_unary": [H, ctypes.c_int32, HP],
     "trsh_scalar": [H, ctypes.c_int32, ctypes.c_float, ctypes.c_int32, HP],
     "trsh_binary": [H, H, ctypes.c_int32, HP],

@@ -282,6 +282,17 @@ class Tensor:
     def ravel(self):
         return self.contiguous().reshape(-1)
 
+    def squeeze(self, dim=None):
+        if dim is None:
+            return self._view(_host.lib().trsh_squeeze, 1, 0)
+        return self._view(_host.lib().trsh_squeeze, 0, int(dim))
+
+    def unbind(self, dim=0):
+        """Slices along the leading dimension (each one a `select(0, i)` view)."""
+        if dim not in (0, -self.dim()) or self.dim() == 0:
+            raise RuntimeError("unbind(): only dim=0 of a tensor with at least one dimension is supported")
+        return tuple(self[i] for i in range(self.shape[0]))
+
     def equal(self, other):
         r = ctypes.c_int32()
         _host.check(_host.lib().trsh_equal(self._h, other._h, ctypes.byref(r)))

@@ -108,3 +108,27 @@ def test_gradients_flow_back_through_reshape_clone_and_contiguous():
     (picked * picked).sum().backward()
     # tests/autograd.rs:1098-1120 (the same mapping without its squeeze step): d/dx x^2 at elements 2 and 5
     assert leaf2.grad.numpy().reshape(-1).tolist() == [0.0, 4.0, 0.0, 0.0, 10.0, 0.0]
+
+
+def test_squeeze_and_unbind_views_and_their_gradients():
+    # the full mapping of tests/autograd.rs:1098-1120: permute -> contiguous -> squeeze -> index -> reshape -> clone
+    leaf = torch.tensor(np.arange(1, 7, dtype=np.float32).reshape(1, 2, 3), device=DEV, requires_grad=True)
+    packed = leaf.permute(2, 0, 1).contiguous()
+    squeezed = packed.squeeze(1)
+    assert squeezed.shape == (3, 2) and squeezed.requires_grad and squeezed.shares_storage_with(packed)
+    cloned = squeezed[1].reshape(2, 1).clone()
+    (cloned * cloned).sum().backward()
+    assert leaf.grad.numpy().reshape(-1).tolist() == [0.0, 4.0, 0.0, 0.0, 10.0, 0.0]
+
+    t = torch.tensor(rnd(1, 1, 4, 1, 5), device=DEV)
+    assert t.squeeze().shape == (4, 5) and t.squeeze().stride() == (5, 1)
+    assert t.squeeze(0).shape == (4, 1, 5) and t.squeeze(1).shape == (1, 4, 1, 5) and t.squeeze(-2).shape == (1, 4, 5)
+    with pytest.raises(IndexError, match="Dimension out of range"):
+        t.squeeze(4)
+
+    w = torch.tensor(rnd(2, 3, 4), device=DEV, requires_grad=True)
+    a, b, c = w.unbind(0)
+    (a * 2.0 + c).sum().backward()
+    want = np.zeros((3, 4), dtype=np.float32)
+    want[0], want[2] = 2.0, 1.0
+    assert np.array_equal(w.grad.numpy(), want)
