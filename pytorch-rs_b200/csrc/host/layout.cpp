@@ -13,7 +13,7 @@ namespace {
 i64 stride_product(i64 stride, i64 dim) {
     // checked_stride_product (src/tensor.rs:4374-4379)
     __int128 p = (__int128)stride * std::max<i64>(dim, 1);
-    if (p > (__int128)INT64_MAX) throw Error(ErrKind::StrideCalculationOverflow, "tensor stride calculation overflowed");
+    if (p > (__int128)INT64_MAX) throw Error(ErrKind::StrideCalculationOverflow, "Stride calculation overflowed");
     return (i64)p;
 }
 
@@ -100,7 +100,7 @@ Shape channels_last_strides(const Shape& shape) {
         out[order[pos]] = stride;
         if (pos < 3) {
             __int128 p = (__int128)stride * shape[order[pos]];
-            if (p > (__int128)INT64_MAX) throw Error(ErrKind::StrideCalculationOverflow, "tensor stride calculation overflowed");
+            if (p > (__int128)INT64_MAX) throw Error(ErrKind::StrideCalculationOverflow, "Stride calculation overflowed");
             stride = (i64)p;
         }
     }
@@ -113,7 +113,7 @@ i64 element_count(const Shape& shape) {
     __int128 n = 1;
     for (i64 d : shape) {
         n *= d;
-        if (n > (__int128)INT64_MAX) throw Error(ErrKind::ElementCountOverflow, "tensor element count overflowed");
+        if (n > (__int128)INT64_MAX) throw Error(ErrKind::ElementCountOverflow, "tensor element count overflowed usize");
     }
     return (i64)n;
 }

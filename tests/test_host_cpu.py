@@ -107,3 +107,16 @@ def test_layout_planner_reference_goldens():
     status = lib.trsh_plan_binary(1, _arr([0]), _arr([1]), 1, _arr([2]), _arr([1]), ctypes.byref(rank), oshape, ostrides)
     assert status == 1
     assert b"The size of tensor a (0) must match the size of tensor b (2) at non-singleton dimension 0" in lib.trsh_last_error()
+
+
+def test_layout_planner_extreme_empty_goldens():
+    import json
+    lib = _host.lib()
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+    for case in gold["extreme_empty_strides"]["cases"]:
+        n = len(case["shape"])
+        out = _arr([0] * n)
+        assert lib.trsh_plan_scalar(n, _arr(case["shape"]), _arr(case["strides"]), out) == 0
+        assert list(out)[:n] == case["scalar_expected"]
+        if "unary_error" in case:
+            assert lib.trsh_plan_unary(n, _arr(case["shape"]), _arr(case["strides"]), out) == 11      # StrideCalculationOverflow

@@ -212,3 +212,54 @@ def test_autograd_goldens_by_composition():
     assert bits(g1) == [z["same_count_bits"]]
     g2 = ref.unbroadcast(np.ones(2, dtype=np.float32), [2], [], RefTensor([-0.0, -0.0], [2]))
     assert bits(g2) == [z["broadcast_bits"]]
+
+
+def test_more_reference_goldens_strides_reshape_reflected_division_and_ordering():
+    r = GOLD["reshape_view_strides"]
+    view = RefTensor(np.arange(24, dtype=np.float32), r["base_shape"]).transpose(*r["transpose"])
+    for case in r["cases"]:
+        out = view.reshape(case["shape"])
+        assert out.strides == case["strides"]
+        assert (view.view_strides(case["shape"]) is not None) == case["shares"]
+    s = GOLD["singleton_channels_last_reshape"]
+    v = RefTensor(np.arange(4, dtype=np.float32), [1, 2, 2, 1], [4, 1, 2, 4])
+    out = v.relu()
+    assert out.strides == s["output_strides"]
+    assert out.reshape(out.shape).strides == s["reshape_same_shape_strides"]
+
+    d = GOLD["reflected_division"]
+    view = RefTensor(d["view"]["values"], d["view"]["shape"], d["view"]["strides"])
+    assert (view / 1.0).strides == d["div_one_strides"]
+    reflected = 1.0 / view
+    assert reflected.strides == d["reflected_strides"] and reflected.logical().reshape(-1).tolist() == d["reflected_values"]
+    for case in d["empty_cases"] + [d["large"]]:
+        assert (1.0 / RefTensor([], case["shape"], case["strides"])).strides == case["expected"]
+    with pytest.raises(ref.RefError) as err:
+        1.0 / RefTensor([], d["extreme_transposed"]["shape"], d["extreme_transposed"]["strides"])
+    assert err.value.kind == d["extreme_transposed"]["error"]
+
+    for case in GOLD["extreme_empty_strides"]["cases"]:
+        assert ref.scalar_strides(case["shape"], case["strides"]) == case["scalar_expected"]
+        if "unary_error" in case:
+            with pytest.raises(ref.RefError) as err:
+                ref.unary_strides(case["shape"], case["strides"])
+            assert err.value.kind == case["unary_error"]
+
+    m = GOLD["matmul_ordering"]
+    out = RefTensor(f32_from_hex(m["left_bits"]), m["left_shape"]).matmul(RefTensor(f32_from_hex(m["right_bits"]), m["right_shape"]))
+    assert bits(out.logical())[0] == m["first_element_bits"]
+
+
+def test_strided_relu_gradients_golden_by_composition():
+    g = GOLD["strided_relu_grads"]
+    storage = np.concatenate([np.full(12, 9.0, dtype=np.float32), f32_from_hex(g["storage_tail_bits"])])
+    source = RefTensor(storage, [2, 3, 4])
+    offset = source.select0(1)
+    grad = np.zeros((2, 3, 4), dtype=np.float32)
+    grad[1] += offset.relu_vjp(np.ones((3, 4), dtype=np.float32))                      # relu(offset).sum()
+    strided = offset.transpose(0, 1)
+    weights = RefTensor(np.arange(1, 13, dtype=np.float32), [4, 3])
+    upstream = ref.unbroadcast(np.ones(12, dtype=np.float32), [4, 3], [4, 3], weights)  # Multiply VJP
+    g_strided = strided.relu_vjp(upstream)                                               # logical [4,3]
+    grad[1] += ref.permute_vjp(g_strided, [3, 4], [1, 0])                                # transpose VJP
+    assert grad.reshape(-1).tolist() == [float(v) for v in g["expected_grad"]]

@@ -314,3 +314,46 @@ def test_refused_allocation_is_reported_like_the_reference():
     with pytest.raises(RuntimeError, match=r"failed to allocate storage for 1099511627776 elements"):
         torch.zeros(1 << 20, 1 << 20, device=DEV)
     assert (torch.ones(4, device=DEV) + 1.0).tolist() == [2.0, 2.0, 2.0, 2.0]
+
+
+def test_more_reference_goldens_on_the_device():
+    g = GOLD["strided_relu_grads"]
+    storage = np.concatenate([np.full(12, 9.0, dtype=np.float32), hexf(g["storage_tail_bits"])]).reshape(2, 3, 4)
+    source = torch.tensor(storage, device=DEV, requires_grad=True)
+    offset = source[1]
+    out = offset.relu()
+    assert out.requires_grad and out.shape == (3, 4) and out.stride() == (4, 1) and out.storage_offset() == 0
+    out.sum().backward()
+    strided = offset.transpose(0, 1)
+    sout = strided.relu()
+    assert sout.shape == (4, 3) and sout.stride() == (1, 4) and not sout.shares_storage_with(strided)
+    weights = torch.tensor(np.arange(1, 13, dtype=np.float32).reshape(4, 3), device=DEV)
+    (sout * weights).sum().backward()
+    assert source.grad.numpy().reshape(-1).tolist() == [float(v) for v in g["expected_grad"]]
+
+    d = GOLD["reflected_division"]
+    view = torch.tensor([[1.0, 2.0]], device=DEV).transpose(0, 1)
+    assert view.shape == (2, 1) and view.stride() == (1, 2)
+    assert (view / 1.0).stride() == tuple(d["div_one_strides"])
+    reflected = 1.0 / view
+    assert reflected.stride() == tuple(d["reflected_strides"]) and reflected.numpy().reshape(-1).tolist() == d["reflected_values"]
+    assert (1.0 / torch.zeros(1, 0, device=DEV).transpose(0, 1)).stride() == (1, 0)
+    assert (1.0 / torch.zeros(1, 0, 1, device=DEV)).stride() == (0, 1, 0)
+    assert (1.0 / torch.zeros(2, 0, 3, device=DEV).transpose(0, 2)).stride() == (2, 2, 1)
+    import sys
+    large = torch.zeros(2, 0, sys.maxsize, device=DEV)
+    assert (1.0 / large).stride() == (0, 1, 0)
+    assert large.transpose(0, 2).stride() == (1, sys.maxsize, sys.maxsize)
+    with pytest.raises(RuntimeError, match="Stride calculation overflowed"):
+        1.0 / large.transpose(0, 1)
+
+    r = GOLD["reshape_view_strides"]
+    v = torch.tensor(np.arange(24, dtype=np.float32).reshape(2, 3, 4), device=DEV).transpose(0, 2)
+    for case in r["cases"]:
+        out = v.reshape(*case["shape"])
+        assert out.stride() == tuple(case["strides"]) and out.shares_storage_with(v) == case["shares"]
+
+    # small matmuls run on the k-ascending FP32 kernel, so the reference's ordering golden holds exactly
+    m = GOLD["matmul_ordering"]
+    out = torch.tensor(hexf(m["left_bits"]).reshape(m["left_shape"]), device=DEV) @ torch.tensor(hexf(m["right_bits"]).reshape(m["right_shape"]), device=DEV)
+    assert bits(out.numpy())[0] == m["first_element_bits"]
