@@ -5,6 +5,8 @@
 // algorithm under float32 matmul precision "highest".  The reference accumulates k ascending
 // with separate multiply and add roundings; this kernel accumulates k ascending per thread with
 // fused multiply-add, which differs by rounding only (tolerance rel 1e-5*sqrt(K) in the tests).
+#include <algorithm>
+
 #include "common.h"
 #include "gemm.h"
 
@@ -22,12 +24,17 @@ __device__ __forceinline__ float ref_relu_vjp(float x, float g) {
 }
 
 template <bool A_KFAST, bool B_NFAST>
-__global__ void __launch_bounds__(256) gemm_simt_kernel(const trs_gemm_desc g, const unsigned int* __restrict__ gate) {
+__global__ void __launch_bounds__(256, 2) gemm_simt_kernel(const trs_gemm_desc g, const unsigned int* __restrict__ gate,
+                                                       const long long tiles_x, const long long tiles_y, const long long total_tiles) {
     if (gate != nullptr && *gate == 0u) return;
     __shared__ __align__(16) float As[2][BK][BM + PAD];
     __shared__ __align__(16) float Bs[2][BK][BN + PAD];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN, batch = blockIdx.z;
+  // Output tiles are walked with a grid stride, so a gated launch can use a small grid.
+  for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const long long tile_x = tile % tiles_x, tile_y = (tile / tiles_x) % tiles_y, batch = tile / (tiles_x * tiles_y);
+    const long long m0 = tile_y * BM, n0 = tile_x * BN;
+    __syncthreads();        // the previous tile's shared-memory reads are done before this tile overwrites them
     const float* __restrict__ A = g.a + batch * g.a_batch_stride;
     const float* __restrict__ B = g.b + batch * g.b_batch_stride;
 
@@ -117,19 +124,22 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const trs_gemm_desc g, c
             C[idx] = v;
         }
     }
+  }
 }
 
 }  // namespace
 
 int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate) {
-    dim3 grid((unsigned)((g.n + BN - 1) / BN), (unsigned)((g.m + BM - 1) / BM), (unsigned)g.batch);
-    if (grid.y > 65535 || grid.z > 65535) return fail(TRS_ERR_UNSUPPORTED, "matmul grid too large for the SIMT kernel");
+    const long long tiles_x = (g.n + BN - 1) / BN, tiles_y = (g.m + BM - 1) / BM, total = tiles_x * tiles_y * g.batch;
+    // A gated launch almost always returns at once: keep its grid small so that the no-op is cheap.
+    const long long cap = gate ? (long long)sm_count(stream->device) * 2 : (1ll << 31) - 1;
+    const unsigned grid = (unsigned)std::max<long long>(1, std::min(total, cap));
     const bool a_kfast = g.a_col_stride == 1 || g.a_row_stride != 1;
     const bool b_nfast = g.b_col_stride == 1 || g.b_row_stride != 1;
-    if (a_kfast && b_nfast) gemm_simt_kernel<true, true><<<grid, 256, 0, stream->stream>>>(g, gate);
-    else if (a_kfast) gemm_simt_kernel<true, false><<<grid, 256, 0, stream->stream>>>(g, gate);
-    else if (b_nfast) gemm_simt_kernel<false, true><<<grid, 256, 0, stream->stream>>>(g, gate);
-    else gemm_simt_kernel<false, false><<<grid, 256, 0, stream->stream>>>(g, gate);
+    if (a_kfast && b_nfast) gemm_simt_kernel<true, true><<<grid, 256, 0, stream->stream>>>(g, gate, tiles_x, tiles_y, total);
+    else if (a_kfast) gemm_simt_kernel<true, false><<<grid, 256, 0, stream->stream>>>(g, gate, tiles_x, tiles_y, total);
+    else if (b_nfast) gemm_simt_kernel<false, true><<<grid, 256, 0, stream->stream>>>(g, gate, tiles_x, tiles_y, total);
+    else gemm_simt_kernel<false, false><<<grid, 256, 0, stream->stream>>>(g, gate, tiles_x, tiles_y, total);
     TRS_CUDA(cudaGetLastError());
     count_launch();
     return TRS_OK;
