@@ -32,8 +32,9 @@ sys.path.insert(0, ROOT)
 N_SIDE = 8192
 ALGO_BYTES = 8 * N_SIDE * N_SIDE + 4 * N_SIDE
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one trs_pw launch on this workload, from the ncu
-# capture summarised in profiles/trs_pw_vector_config2.md (writes still dirty in L2 are not counted).
+# dram__bytes_read.sum + dram__bytes_write.sum of one trs_pw launch on this workload, from an ncu
+# capture of exactly this kernel and size (its summary is kept under profiles/); writes that are
+# still dirty in L2 when the kernel ends are not counted.
 NCU_DRAM_BYTES_PER_LAUNCH = 484834304
 
 
