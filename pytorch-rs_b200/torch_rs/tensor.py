@@ -193,6 +193,17 @@ class Tensor:
         a = self.numpy()
         return a if dtype is None else a.astype(dtype)
 
+    def __dlpack__(self, stream=None):
+        """Zero-copy export; pending work is enqueued first and the engine's stream is drained, so the
+        consumer may use the memory on any stream."""
+        from . import _dlpack
+        capsule = _dlpack.to_dlpack(self)
+        _host.check(_host.lib().trsh_sync(self.device.index))
+        return capsule
+
+    def __dlpack_device__(self):
+        return (2, self.device.index)          # kDLCUDA
+
     def tolist(self):
         return self.numpy().tolist()
 

@@ -357,3 +357,16 @@ def test_more_reference_goldens_on_the_device():
     m = GOLD["matmul_ordering"]
     out = torch.tensor(hexf(m["left_bits"]).reshape(m["left_shape"]), device=DEV) @ torch.tensor(hexf(m["right_bits"]).reshape(m["right_shape"]), device=DEV)
     assert bits(out.numpy())[0] == m["first_element_bits"]
+
+
+def test_dlpack_export_is_zero_copy_and_keeps_the_layout():
+    pt = pytest.importorskip("torch")
+    xs = rnd(18, 6, 10)
+    view = torch.tensor(xs, device=DEV).T                  # [10,6], strides (1,10)
+    out = view * 2.0                                                                             # pending until exported
+    shared = pt.from_dlpack(out)
+    assert shared.device.type == "cuda" and tuple(shared.shape) == (10, 6) and tuple(shared.stride()) == out.stride()
+    assert shared.data_ptr() == out.data_ptr()
+    assert np.array_equal(shared.cpu().numpy(), (xs.T * 2.0).astype(np.float32))
+    del out                     # the capsule keeps the storage alive
+    assert np.array_equal(shared.cpu().numpy(), (xs.T * 2.0).astype(np.float32))
