@@ -32,6 +32,8 @@ sys.path.insert(0, ROOT)
 N_SIDE = 8192
 ALGO_BYTES = 8 * N_SIDE * N_SIDE + 4 * N_SIDE
 FALLBACK_HBM_GBS = 6650.0
+WORKLOAD_TEXT = ("exp(2.0*relu(x.mT+b))-x.mT, x f32 [8192,8192] via transposed view, b [8192] broadcast, scalar 2.0; "
+                 "one pass of the whole chain per step, per GPU")
 # dram__bytes_read.sum + dram__bytes_write.sum of one trs_pw launch on this workload, from an ncu
 # capture of exactly this kernel and size (its summary is kept under profiles/); writes that are
 # still dirty in L2 when the kernel ends are not counted.
@@ -148,8 +150,8 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "fused pointwise GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "exp(2.0*relu(x.mT+b))-x.mT, x f32 [8192,8192] via transposed view, b [8192] broadcast",
-                   "sample": sample},
+        "config": {"workload": WORKLOAD_TEXT, "l2": "inputs+outputs 512 MiB per step, larger than the 126 MB L2",
+                   "parallelism": f"dp{args.gpus}", "algorithmic_bytes_per_step_per_gpu": ALGO_BYTES, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample,
                          "host_cores": os.cpu_count()},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -334,8 +336,7 @@ def run_ours(args, rank, world, local_rank):
         "metric": "fused pointwise GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "exp(2.0*relu(x.mT+b))-x.mT, x f32 [8192,8192] via transposed view, b [8192] broadcast, "
-                               "one fused kernel per step, per GPU",
+        "config": {"workload": WORKLOAD_TEXT,
                    "l2": "inputs+outputs 512 MiB per step, larger than the 126 MB L2", "parallelism": f"dp{world}",
                    "algorithmic_bytes_per_step_per_gpu": ALGO_BYTES},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
