@@ -340,9 +340,10 @@ struct SplitArgs {
     long long batch_stride, row_stride, k_stride;     // source strides in elements
     long long rows, k, k_pad;
     unsigned int* nonfinite;
+    int lo_only;          // the source itself serves as the hi operand (the MMA drops the low 13 bits): hi = truncation
 };
 
-__device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsigned int* nonfinite) {
+__device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsigned int* nonfinite, bool truncate_hi = false) {
     const uint32_t bits = __float_as_uint(a);
     if ((bits & 0x7f800000u) == 0x7f800000u) {         // inf / NaN: not representable by the split
         atomicOr(nonfinite, 1u);
@@ -350,8 +351,12 @@ __device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsig
         return;
     }
     uint32_t h;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
-    if ((h & 0x7f800000u) == 0x7f800000u) h = bits & 0xffffe000u;   // rounding overflowed: truncate instead
+    if (truncate_hi) {
+        h = bits & 0xffffe000u;
+    } else {
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+        if ((h & 0x7f800000u) == 0x7f800000u) h = bits & 0xffffe000u;   // rounding overflowed: truncate instead
+    }
     hi = __uint_as_float(h);
     const float rest = __fsub_rn(a, hi);                // exact
     uint32_t l;
@@ -380,8 +385,8 @@ __global__ void __launch_bounds__(256) split_tf32_kfast_kernel(const SplitArgs a
         }
         float h[4], l[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) split_value(v[e], h[e], l[e], a.nonfinite);
-        *reinterpret_cast<float4*>(hi + r * a.k_pad + k0) = make_float4(h[0], h[1], h[2], h[3]);
+        for (int e = 0; e < 4; ++e) split_value(v[e], h[e], l[e], a.nonfinite, a.lo_only != 0);
+        if (!a.lo_only) *reinterpret_cast<float4*>(hi + r * a.k_pad + k0) = make_float4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<float4*>(lo + r * a.k_pad + k0) = make_float4(l[0], l[1], l[2], l[3]);
     }
 }
@@ -466,11 +471,13 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long k_pad, long long batch, int box_rows) {
+int32_t make_operand_map(CUtensorMap* map, const float* base, long long rows, long long k_extent, long long batch,
+                         long long row_stride, long long batch_stride, int box_rows) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[3] = {(cuuint64_t)k_pad, (cuuint64_t)rows, (cuuint64_t)batch};
-    cuuint64_t strides[2] = {(cuuint64_t)k_pad * 4, (cuuint64_t)rows * (cuuint64_t)k_pad * 4};
+    cuuint64_t dims[3] = {(cuuint64_t)k_extent, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)batch_stride * 4};
+    void* plane = const_cast<float*>(base);
     cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
     const CUtensorMapSwizzle swizzle = ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (ROW_BYTES == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     cuuint32_t estr[3] = {1, 1, 1};
@@ -504,9 +511,25 @@ int32_t device_words(int device, DeviceWords** out) {
     return TRS_OK;
 }
 
+int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long k_pad, long long batch, int box_rows) {
+    return make_operand_map(map, plane, rows, k_pad, batch, k_pad, rows * k_pad, box_rows);
+}
+
+// Whether the MMA can read the hi operand straight from the source (K-major, 16-byte aligned
+// rows).  kind::tf32 ignores the low 13 mantissa bits of its FP32 operands, i.e. it sees
+// hi = truncation(a); the lo plane is then tf32(a - truncation(a)) and no hi plane is written.
+// (Checked on B200 with operands whose low 13 bits are all ones: results stay within 4e-6*sqrt(K)*rms
+// of a float64 product, which a rounding MMA would miss by orders of magnitude.)
+bool raw_hi_ok(const float* src, long long batch, long long rows, long long batch_stride, long long row_stride, long long k_stride, long long k) {
+    if (k_stride != 1 || (reinterpret_cast<uintptr_t>(src) & 15u) != 0 || row_stride % 4 != 0 || row_stride < k) return false;
+    if (batch > 1 && (batch_stride % 4 != 0 || batch_stride < rows * row_stride)) return false;
+    return true;
+}
+
 int32_t launch_split(const float* src, long long batch, long long rows, long long k, long long k_pad, long long batch_stride,
-                     long long row_stride, long long k_stride, float* hi, float* lo, unsigned int* nonfinite, trs_stream stream) {
-    SplitArgs a{src, hi, lo, batch_stride, row_stride, k_stride, rows, k, k_pad, nonfinite};
+                     long long row_stride, long long k_stride, float* hi, float* lo, unsigned int* nonfinite, trs_stream stream,
+                     int lo_only = 0) {
+    SplitArgs a{src, hi, lo, batch_stride, row_stride, k_stride, rows, k, k_pad, nonfinite, lo_only};
     if (k_stride == 1 || k == 1) {
         const int vec = (row_stride % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
         const long long total = rows * (k_pad >> 2);
@@ -552,12 +575,16 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     float* b_lo = b_hi + b_plane;
     TRS_CUDA(cudaMemsetAsync(words->nonfinite, 0, sizeof(unsigned int), stream->stream));
     // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
-    TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream));
-    TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream));
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-    TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM));
+    bool a_raw = raw_hi_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
+    bool b_raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
+    if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM) != TRS_OK) a_raw = false;
+    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, BN) != TRS_OK) b_raw = false;
+    TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
+    TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
+    if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM));
     TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM));
-    TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, BN));
+    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, BN));
     TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, BN));
     const long long tiles_m = (g.m + BM - 1) / BM, tiles_n = (g.n + BN - 1) / BN;
     const long long total_tiles = tiles_m * tiles_n * g.batch;

@@ -128,3 +128,21 @@ def test_tensor_core_path_keeps_inf_nan_classification():
     finite = np.isfinite(want)
     assert np.array_equal(np.sign(c[np.isinf(want)]), np.sign(want[np.isinf(want)]))
     assert np.allclose(c[finite], want[finite], rtol=1e-4, atol=1e-4)
+
+
+def test_tensor_core_path_with_low_mantissa_bits_all_set():
+    # The K-major operand is fed to the MMA unsplit (the MMA drops the low 13 mantissa bits) and only the
+    # remainder plane is prepared.  Operands whose low 13 bits are all ones are the worst case for that:
+    # if the hardware rounded instead of truncating, every product would be off by about 2^-11.
+    m, n, k = 256, 256, 512
+    rng = np.random.default_rng(30)
+    a = (rng.standard_normal((m, k)).astype(np.float32).view(np.uint32) | np.uint32(0x1FFF)).view(np.float32)
+    bt = (rng.standard_normal((n, k)).astype(np.float32).view(np.uint32) | np.uint32(0x1FFF)).view(np.float32)
+    ra, rb = RefTensor.from_numpy(a), RefTensor.from_numpy(bt).mT          # both operands K-major
+    c, _ = run(ra, rb, "tcgen05_3xtf32")
+    ref64 = a.astype(np.float64) @ bt.astype(np.float64).T
+    rms = np.sqrt(np.mean(ref64 ** 2))
+    assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * rms
+    # and the same product with a transposed (pre-split) right operand agrees to the same bound
+    c2, _ = run(ra, RefTensor.from_numpy(np.ascontiguousarray(bt.T)), "tcgen05_3xtf32")
+    assert np.abs(c2 - ref64).max() <= 4e-6 * np.sqrt(k) * rms
