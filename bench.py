@@ -198,6 +198,8 @@ def run_ours(args, rank, world, local_rank):
         return float(t.item())
 
     dev = f"cuda:{local_rank}"
+    from torch_rs import distributed as tdist
+    numa_node = tdist.bind_to_device_numa_node(local_rank)     # staging memory local to this GPU's PCIe root
     raw = ctypes.c_void_p()
     _host.check(_host.lib().trsh_stream(local_rank, ctypes.byref(raw)))
     stream = Stream.__new__(Stream)
@@ -343,7 +345,8 @@ def run_ours(args, rank, world, local_rank):
                      "traffic": traffic, "peak_source": f"of {peak_kind}", "kernel": "trs_pw (vector class)"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ALGO_BYTES // 2 + 2 * N_SIDE,
                 "d2h_bytes_per_step": 4 * N_SIDE * N_SIDE, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "how": f"pinned host buffers; {E2E_SLABS} row slabs per step so uploads, kernels and read-backs overlap"},
+                "how": f"pinned host buffers; {E2E_SLABS} row slabs per step so uploads, kernels and read-backs overlap",
+                "numa_node": numa_node},
         "gpu_launches": launches, "clocks": clock_info, "parity": parity, "extra": extra,
     }
     if cpu_baseline is not None:

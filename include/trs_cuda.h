@@ -133,6 +133,8 @@ typedef struct trs_gemm_desc {
  * New relative to the reference, whose Device has the single variant Cpu (src/device.rs:5-9)
  * and whose Storage owns a Vec<f32> (src/storage.rs:7-18, 116-134). */
 int32_t trs_device_count(int32_t* count);
+/* PCI bus id ("0000:1b:00.0") of a device, for placing host staging memory on the device's NUMA node. */
+int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length);
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr);       /* cached blocks; Storage::from_owned */
 int32_t trs_free(int32_t device, void* ptr);                        /* Storage drop */
 int32_t trs_empty_cache(int32_t device);

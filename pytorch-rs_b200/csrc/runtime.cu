@@ -76,6 +76,12 @@ int32_t trs_device_count(int32_t* count) {
     return TRS_OK;
 }
 
+int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length) {
+    if (!buffer || length < 16) return fail(TRS_ERR_INVALID_ARGUMENT, "buffer of at least 16 bytes needed");
+    TRS_CUDA(cudaDeviceGetPCIBusId(buffer, length, device));
+    return TRS_OK;
+}
+
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) {
     if (!ptr || device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad trs_malloc arguments");
     *ptr = nullptr;

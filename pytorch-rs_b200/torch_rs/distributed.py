@@ -70,6 +70,40 @@ def barrier() -> None:
         dist.barrier()
 
 
+def _parse_cpu_list(text: str) -> set[int]:
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_to_device_numa_node(device_index: int) -> int | None:
+    """Pin this process to the CPUs of the NUMA node its GPU hangs off, so that page-locked staging
+    buffers allocated afterwards are local to that GPU's PCIe root (host<->device copies of several
+    ranks then stop contending for one socket's memory).  Returns the node, or None when unknown."""
+    import ctypes
+    from . import _abi
+    buf = ctypes.create_string_buffer(32)
+    if _abi.lib().trs_device_pci_bus_id(device_index, buf, 32) != 0:
+        return None
+    bus = buf.value.decode().lower()
+    try:
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = _parse_cpu_list(open(f"/sys/devices/system/node/node{node}/cpulist").read())
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError):
+        return None
+
+
 def shard_bounds(total: int, rank: int, world: int) -> tuple[int, int]:
     """Contiguous [begin, end) slab of `total` rows/batches for `rank`: the first `total % world`
     ranks get one extra, so slabs differ by at most one and cover everything exactly once."""

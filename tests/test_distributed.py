@@ -67,3 +67,13 @@ def test_data_parallel_mlp_gradients_match_single_gpu(tmp_path):
     assert r["world"] == 2
     assert r["worst_error_over_bound"] <= 1.0
     assert abs(r["loss"] - r["full_loss"]) <= 1e-4 * abs(r["full_loss"]) + 1e-3
+
+
+def test_cpu_list_parsing_and_numa_binding_without_a_device():
+    assert dist._parse_cpu_list("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert dist._parse_cpu_list("") == set()
+    import torch_rs as torch
+    if not torch.cuda.is_available():
+        before = os.sched_getaffinity(0)
+        assert dist.bind_to_device_numa_node(0) is None          # no device: nothing is changed
+        assert os.sched_getaffinity(0) == before
