@@ -112,7 +112,8 @@ typedef enum trs_epilogue {
 typedef enum trs_gemm_algo {
     TRS_GEMM_AUTO = 0,
     TRS_GEMM_SIMT_FP32 = 1,      /* register-tiled FFMA kernel, any strides          */
-    TRS_GEMM_TCGEN05_3XTF32 = 2  /* TMA + tcgen05.mma kind::tf32, 3-product split     */
+    TRS_GEMM_TCGEN05_3XTF32 = 2,      /* TMA + tcgen05.mma kind::tf32, 3-product split, one CTA per 128x256 tile */
+    TRS_GEMM_TCGEN05_3XTF32_2CTA = 3  /* same product, cta_group::2: a CTA pair per 256x256 tile                 */
 } trs_gemm_algo;
 
 /* Batched float32 matmul C[b] = A[b] @ B[b].  All strides in elements.  Replaces

@@ -12,7 +12,7 @@ int32_t validate(const trs_gemm_desc* g) {
     if ((g->epilogue == TRS_EPI_BIAS || g->epilogue == TRS_EPI_BIAS_RELU) && !g->bias) return fail(TRS_ERR_INVALID_ARGUMENT, "bias epilogue without bias");
     if (g->epilogue == TRS_EPI_RELU_VJP && !g->aux) return fail(TRS_ERR_INVALID_ARGUMENT, "relu_vjp epilogue without aux");
     if (g->batch * g->m * g->n != 0 && (!g->c || (g->k != 0 && (!g->a || !g->b)))) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL matrix pointer");
-    if (g->algo < TRS_GEMM_AUTO || g->algo > TRS_GEMM_TCGEN05_3XTF32) return fail(TRS_ERR_INVALID_ARGUMENT, "unknown algo %d", g->algo);
+    if (g->algo < TRS_GEMM_AUTO || g->algo > TRS_GEMM_TCGEN05_3XTF32_2CTA) return fail(TRS_ERR_INVALID_ARGUMENT, "unknown algo %d", g->algo);
     return TRS_OK;
 }
 }  // namespace
@@ -22,10 +22,12 @@ extern "C" {
 int32_t trs_matmul_select_algo(const trs_gemm_desc* desc, int32_t* algo) {
     TRS_TRY(validate(desc));
     if (!algo) return fail(TRS_ERR_INVALID_ARGUMENT, "algo is NULL");
-    if (desc->algo == TRS_GEMM_TCGEN05_3XTF32 && !gemm_tc_eligible(*desc))
+    const bool tensor_core = desc->algo == TRS_GEMM_TCGEN05_3XTF32 || desc->algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
+    if (tensor_core && !gemm_tc_eligible(*desc))
         return fail(TRS_ERR_UNSUPPORTED, "descriptor does not meet the tensor-core path's alignment rules");
     if (desc->algo != TRS_GEMM_AUTO) { *algo = desc->algo; return TRS_OK; }
-    *algo = gemm_tc_eligible(*desc) ? TRS_GEMM_TCGEN05_3XTF32 : TRS_GEMM_SIMT_FP32;
+    if (!gemm_tc_eligible(*desc)) *algo = TRS_GEMM_SIMT_FP32;
+    else *algo = gemm_tc_pair_preferred(*desc) ? TRS_GEMM_TCGEN05_3XTF32_2CTA : TRS_GEMM_TCGEN05_3XTF32;
     return TRS_OK;
 }
 
@@ -38,7 +40,11 @@ int32_t trs_matmul_f32(const trs_gemm_desc* desc, trs_stream stream) {
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", stream->device);
     // k == 0: the product is the zero matrix (reference: zero-filled output, src/tensor.rs:2473);
     // the SIMT kernel handles it (no k tiles) including the epilogue.
-    if (algo == TRS_GEMM_TCGEN05_3XTF32 && desc->k > 0) return gemm_tc_launch(*desc, stream);
+    if ((algo == TRS_GEMM_TCGEN05_3XTF32 || algo == TRS_GEMM_TCGEN05_3XTF32_2CTA) && desc->k > 0) {
+        trs_gemm_desc chosen = *desc;
+        chosen.algo = algo;
+        return gemm_tc_launch(chosen, stream);
+    }
     return gemm_simt_launch(*desc, stream);
 }
 

@@ -94,6 +94,42 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- two-CTA (cta_group::2) variants: the CTA pair of a cluster works on one 256x256 tile ----------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Cluster-window address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Load into this CTA's shared memory; the bytes are counted on `cluster_bar`, the leader CTA's barrier.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// kind::tf32, FP32 accumulate, A and B K-major, M=256 over the CTA pair (128 rows each), N=256.
+constexpr uint32_t kInstrDescPair = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p; }"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(kInstrDescPair), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in every CTA of `cta_mask` once the MMAs issued so far retire.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
 __device__ __forceinline__ float ref_relu(float v) {
     return ((__float_as_uint(v) & 0x7fffffffu) == 0u) ? v : fmaxf(v, 0.0f);
 }
@@ -116,15 +152,15 @@ struct EpilogueArgs {
 
 // Tile order: bands of 16 tile rows, walked column by column, so that the ~148 tiles in flight at
 // any time cover a roughly square 16 x 9 patch of C and share their A and B panels in L2.
-constexpr int GROUP_M = 16;
+template <int kGroup = 16>
 __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& batch, int& tile_m, int& tile_n) {
     const int per_batch = tiles_m * tiles_n;
     batch = t / per_batch;
     const int rem = t - batch * per_batch;
-    const int band = rem / (GROUP_M * tiles_n);
-    const int first_m = band * GROUP_M;
-    const int band_rows = min(GROUP_M, tiles_m - first_m);
-    const int in_band = rem - band * GROUP_M * tiles_n;
+    const int band = rem / (kGroup * tiles_n);
+    const int first_m = band * kGroup;
+    const int band_rows = min(kGroup, tiles_m - first_m);
+    const int in_band = rem - band * kGroup * tiles_n;
     tile_n = in_band / band_rows;
     tile_m = first_m + (in_band - tile_n * band_rows);
 }
@@ -140,6 +176,80 @@ __device__ __forceinline__ void decode_item(int w, const EpilogueArgs& e, int& t
     kb_begin = (r & 1) ? mid : 0;
     kb_end = (r & 1) ? e.k_blocks : mid;
     split = true;
+}
+
+// Epilogue of one warp for one tile: reads its 32 accumulator rows (TMEM lanes) 32 columns at a time,
+// hands the accumulator back as soon as the last columns are in registers, applies the fused
+// epilogue and stores.  `tmem_acc` addresses the warp's lanes at the accumulator's first column;
+// `empty_bar_addr` is the accumulator-empty barrier (a cluster address of the leader's barrier when kPair).
+template <bool kPair>
+__device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_t tmem_acc, long long row, long long batch_off, int tile_n,
+                                                  bool split, bool vec_ok, int lane, uint32_t empty_bar_addr) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_acc + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 == BN) {
+            // every column of this accumulator has been read into registers: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) { if (kPair) mbar_arrive_cluster(empty_bar_addr); else mbar_arrive(empty_bar_addr); }
+        }
+        const long long col0 = (long long)tile_n * BN + c0;
+        if (row < e.m && col0 < e.n) {
+            const long long idx0 = batch_off + row * e.c_row_stride + col0;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            const bool full_cols = col0 + 32 <= e.n;
+            if (e.epilogue == TRS_EPI_BIAS || e.epilogue == TRS_EPI_BIAS_RELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (full_cols || col0 + j < e.n) v[j] = __fadd_rn(v[j], __ldg(e.bias + col0 + j));
+            }
+            if (e.epilogue == TRS_EPI_BIAS_RELU && e.preact) {
+                if (full_cols && vec_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.preact + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else {
+                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.preact[idx0 + j] = v[j];
+                }
+            }
+            if (e.epilogue == TRS_EPI_BIAS_RELU || e.epilogue == TRS_EPI_RELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = ref_relu(v[j]);
+            }
+            if (e.epilogue == TRS_EPI_RELU_VJP) {
+                if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.aux) & 15u) == 0)) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 z = __ldcs(reinterpret_cast<const float4*>(e.aux + idx0 + j));
+                        v[j] = ref_relu_vjp(z.x, v[j]); v[j + 1] = ref_relu_vjp(z.y, v[j + 1]);
+                        v[j + 2] = ref_relu_vjp(z.z, v[j + 2]); v[j + 3] = ref_relu_vjp(z.w, v[j + 3]);
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
+                }
+            }
+            if (split) {
+                // half-K partial (plain product only): add onto the zeroed output
+                for (int j = 0; j < 32; ++j) if (col0 + j < e.n) atomicAdd(e.c + idx0 + j, v[j]);
+            } else if (full_cols && vec_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+                for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.c[idx0 + j] = v[j];
+            }
+        }
+    }
 }
 
 // Persistent kernel: CTA i works on tiles i, i + gridDim.x, ...; the accumulator of tile j lives
@@ -254,71 +364,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long row = (long long)tile_m * BM + quarter * 32 + lane;
             const long long batch_off = (long long)batch * e.c_batch_stride;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(taddr) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c0 + 32 == BN) {
-                    // every column of this accumulator has been read into registers: hand it back
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
-                }
-                const long long col0 = (long long)tile_n * BN + c0;
-                if (row < e.m && col0 < e.n) {
-                    const long long idx0 = batch_off + row * e.c_row_stride + col0;
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    const bool full_cols = col0 + 32 <= e.n;
-                    if (e.epilogue == TRS_EPI_BIAS || e.epilogue == TRS_EPI_BIAS_RELU) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) if (full_cols || col0 + j < e.n) v[j] = __fadd_rn(v[j], __ldg(e.bias + col0 + j));
-                    }
-                    if (e.epilogue == TRS_EPI_BIAS_RELU && e.preact) {
-                        if (full_cols && vec_ok) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.preact + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-                            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.preact[idx0 + j] = v[j];
-                        }
-                    }
-                    if (e.epilogue == TRS_EPI_BIAS_RELU || e.epilogue == TRS_EPI_RELU) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = ref_relu(v[j]);
-                    }
-                    if (e.epilogue == TRS_EPI_RELU_VJP) {
-                        if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.aux) & 15u) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 z = __ldcs(reinterpret_cast<const float4*>(e.aux + idx0 + j));
-                                v[j] = ref_relu_vjp(z.x, v[j]); v[j + 1] = ref_relu_vjp(z.y, v[j + 1]);
-                                v[j + 2] = ref_relu_vjp(z.z, v[j + 2]); v[j + 3] = ref_relu_vjp(z.w, v[j + 3]);
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
-                        }
-                    }
-                    if (split) {
-                        // half-K partial (plain product only): add onto the zeroed output
-                        for (int j = 0; j < 32; ++j) if (col0 + j < e.n) atomicAdd(e.c + idx0 + j, v[j]);
-                    } else if (full_cols && vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.c[idx0 + j] = v[j];
-                    }
-                }
-            }
+            drain_accumulator<false>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, split, vec_ok, lane,
+                                     smem_u32(&acc_empty[acc]));
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -327,6 +374,156 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+// ---- two-CTA kernel --------------------------------------------------------------------------------
+// A cluster of two CTAs (neighbouring SMs) owns one 256x256 tile: CTA r stages its own 128 rows of
+// A and rows [128 r, 128 r + 128) of the B^T tile, so every byte of B is staged once per pair
+// instead of once per CTA, and each SM's shared memory serves 8 KiB per MMA instead of 12 KiB (the
+// one-CTA kernel is bound by exactly that port).  The leader (rank 0) issues every MMA
+// (tcgen05.mma.cta_group::2, M=256); each CTA's tensor core accumulates its own 128 rows in its own
+// TMEM, and each CTA's epilogue warps drain and store them.
+//   stage full   (leader only)  one arrive.expect_tx by the leader's producer for the bytes of both CTAs
+//   stage empty  (each CTA)     one multicast tcgen05.commit by the leader's MMA thread
+//   acc full     (each CTA)     one multicast tcgen05.commit by the leader's MMA thread
+//   acc empty    (leader only)  eight arrivals: the four epilogue warps of both CTAs
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_TILE_BYTES = (BN / 2) * ROW_BYTES;
+constexpr int PAIR_STAGE_BYTES = 2 * A_TILE_BYTES + 2 * PAIR_B_TILE_BYTES;       // 32 KiB per CTA
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_GROUP_M = 8;                                                   // bands of 8 x 256 rows
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                        const EpilogueArgs e) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + PAIR_STAGES;
+    uint64_t* acc_full = bars + 2 * PAIR_STAGES;
+    uint64_t* acc_empty = bars + 2 * PAIR_STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PAIR_STAGES + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();             // 0: leader
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                   // the peer's barriers are initialised before anything signals them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer (both CTAs) ----
+            bool failed = false;
+            uint32_t g = 0;
+            for (int w = pair; w < e.total_items && !failed; w += pairs) {
+                int t, kb_begin, kb_end, batch, tile_m, tile_n;
+                bool split;
+                decode_item(w, e, t, kb_begin, kb_end, split);
+                decode_tile<PAIR_GROUP_M>(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
+                const int a_row = tile_m * (2 * BM) + (int)rank * BM;
+                const int b_row = tile_n * BN + (int)rank * (BN / 2);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
+                    const uint32_t s = g % PAIR_STAGES, round = g / PAIR_STAGES;
+                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1)) { failed = true; break; }
+                    const uint32_t full = map_to_cta(smem_u32(&full_bar[s]), 0);
+                    const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
+                    tma_load_3d_pair(base, &map_a_hi, full, kb * BK, a_row, batch);
+                    tma_load_3d_pair(base + A_TILE_BYTES, &map_a_lo, full, kb * BK, a_row, batch);
+                    tma_load_3d_pair(base + 2 * A_TILE_BYTES, &map_b_hi, full, kb * BK, b_row, batch);
+                    tma_load_3d_pair(base + 2 * A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, kb * BK, b_row, batch);
+                }
+            }
+            // stay until the leader's last commits have arrived on this CTA's barriers
+            const uint32_t last = g < (uint32_t)PAIR_STAGES ? g : (uint32_t)PAIR_STAGES;
+            for (uint32_t u = g - last; u < g && !failed; ++u)
+                if (!mbar_wait(smem_u32(&empty_bar[u % PAIR_STAGES]), (u / PAIR_STAGES) & 1)) failed = true;
+            if (failed) atomicExch(&g_gemm_error, 4u);
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (leader CTA only) ----
+            bool failed = false;
+            uint32_t g = 0, it = 0;
+            for (int w = pair; w < e.total_items && !failed; w += pairs, ++it) {
+                int t, kb_begin, kb_end;
+                bool split;
+                decode_item(w, e, t, kb_begin, kb_end, split);
+                const uint32_t acc = it & 1, use = it >> 1;
+                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
+                    const uint32_t s = g % PAIR_STAGES;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / PAIR_STAGES) & 1)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
+                    const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
+                    const uint64_t b_hi = smem_desc(base + 2 * A_TILE_BYTES), b_lo = smem_desc(base + 2 * A_TILE_BYTES + PAIR_B_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 8; ++k) {
+                        const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);
+                        umma_tf32_pair(d, a_lo + step, b_hi + step, (kb != kb_begin) || (k != 0));
+                        umma_tf32_pair(d, a_hi + step, b_lo + step, 1u);
+                        umma_tf32_pair(d, a_hi + step, b_hi + step, 1u);
+                    }
+                    umma_commit_pair(smem_u32(&empty_bar[s]), 3);
+                }
+                umma_commit_pair(smem_u32(&acc_full[acc]), 3);
+            }
+            // stay until the peer's epilogue has made its last arrivals on this CTA's barriers
+            const uint32_t last = it < 2u ? it : 2u;
+            for (uint32_t j = it - last; j < it && !failed; ++j)
+                if (!mbar_wait(smem_u32(&acc_empty[j & 1]), (j >> 1) & 1)) failed = true;
+            if (failed) atomicExch(&g_gemm_error, 5u);
+        }
+    } else {
+        // ---- epilogue warps 2..5 of both CTAs: this CTA's 128 rows of the tile ----
+        const int quarter = warp & 3;
+        const bool vec_ok = (e.c_row_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.c) & 15u) == 0) && (e.c_batch_stride % 4 == 0) &&
+                            (!e.preact || (reinterpret_cast<uintptr_t>(e.preact) & 15u) == 0);
+        uint32_t it = 0;
+        for (int w = pair; w < e.total_items; w += pairs, ++it) {
+            int t, kb_begin, kb_end, batch, tile_m, tile_n;
+            bool split;
+            decode_item(w, e, t, kb_begin, kb_end, split);
+            decode_tile<PAIR_GROUP_M>(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
+            const uint32_t acc = it & 1, use = it >> 1;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1)) {
+                if (lane == 0) atomicExch(&g_gemm_error, 6u);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const long long row = (long long)tile_m * (2 * BM) + (long long)rank * BM + quarter * 32 + lane;
+            const long long batch_off = (long long)batch * e.c_batch_stride;
+            drain_accumulator<true>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, split, vec_ok, lane,
+                                    map_to_cta(smem_u32(&acc_empty[acc]), 0));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                   // neither CTA frees tensor memory or exits while the other may still signal it
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -492,6 +689,7 @@ struct DeviceWords {
     unsigned int* nonfinite = nullptr;
     bool launched = false;
     bool smem_set = false;
+    int pair_clusters = 0;      // CTA pairs of the two-CTA kernel that can be resident at once
 };
 DeviceWords g_words[16];
 std::mutex g_words_mu;
@@ -505,6 +703,20 @@ int32_t device_words(int device, DeviceWords** out) {
     }
     if (!w.smem_set) {
         TRS_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TRS_CUDA(cudaFuncSetAttribute(gemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
+        const int sms = sm_count(device);
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sms / 2 * 2)); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tf32x3_pair_kernel, &cfg) != cudaSuccess || clusters < 1) {
+            cudaGetLastError();
+            clusters = sms / 2;
+        }
+        w.pair_clusters = std::min(clusters, sms / 2);
         w.smem_set = true;
     }
     *out = &w;
@@ -549,7 +761,18 @@ int32_t launch_split(const float* src, long long batch, long long rows, long lon
     return TRS_OK;
 }
 
+// Whether AUTO takes the two-CTA kernel: it pays in 256-row tiles, so it wants at most one eighth
+// of the rows it computes to be padding.
+constexpr bool kPairDefault = false;
+
 }  // namespace
+
+bool gemm_tc_pair_preferred(const trs_gemm_desc& g) {
+    if (!kPairDefault) return false;
+    const long long padded = (g.m + 2 * BM - 1) / (2 * BM) * (2 * BM);
+    const long long single = (g.m + BM - 1) / BM * BM;
+    return padded * 8 <= single * 9;
+}
 
 bool gemm_tc_eligible(const trs_gemm_desc& g) {
     if (g.batch < 1 || g.batch > 65535 || g.k < 32 || g.m < 1 || g.n < 1) return false;
@@ -576,33 +799,38 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     TRS_CUDA(cudaMemsetAsync(words->nonfinite, 0, sizeof(unsigned int), stream->stream));
     // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    const bool pair = g.algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
+    const int b_box = pair ? BN / 2 : BN;                // B^T rows one CTA stages
     bool a_raw = raw_hi_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
     bool b_raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
     if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM) != TRS_OK) a_raw = false;
-    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, BN) != TRS_OK) b_raw = false;
+    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box) != TRS_OK) b_raw = false;
     TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
     TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
     if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM));
     TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM));
-    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, BN));
-    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, BN));
-    const long long tiles_m = (g.m + BM - 1) / BM, tiles_n = (g.n + BN - 1) / BN;
+    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box));
+    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box));
+    const long long tile_rows = pair ? 2 * BM : BM;
+    const long long tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + BN - 1) / BN;
     const long long total_tiles = tiles_m * tiles_n * g.batch;
     if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
     EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / BK), g.epilogue,
                    (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles};
-    const long long sms = sm_count(stream->device);
-    // A last round that occupies at most half of the SMs is cut in two along K (plain products on
+    // units that work side by side: SMs, or resident CTA pairs
+    const long long units = pair ? words->pair_clusters : sm_count(stream->device);
+    // A last round that occupies at most half of the units is cut in two along K (plain products on
     // a dense C only): 512 tiles on 148 SMs then take 3.5 instead of 4 tile times.
-    const long long tail = total_tiles % sms;
+    const long long tail = total_tiles % units;
     const bool dense_c = g.c_row_stride == g.n && (g.batch == 1 || g.c_batch_stride == g.m * g.n);
-    if (g.epilogue == TRS_EPI_NONE && total_tiles > sms && tail > 0 && tail * 2 <= sms && e.k_blocks >= 16 && dense_c) {
+    if (g.epilogue == TRS_EPI_NONE && total_tiles > units && tail > 0 && tail * 2 <= units && e.k_blocks >= 16 && dense_c) {
         e.whole_tiles = (int)(total_tiles - tail);
         e.total_items = (int)(e.whole_tiles + 2 * tail);
         TRS_CUDA(cudaMemsetAsync(g.c, 0, (size_t)(g.batch * g.m * g.n) * sizeof(float), stream->stream));
     }
-    const unsigned grid = (unsigned)std::min<long long>(e.total_items, sms);
-    gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
+    const unsigned grid = (unsigned)std::min<long long>(e.total_items, units);
+    if (pair) gemm_tf32x3_pair_kernel<<<2 * grid, 192, PAIR_SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
+    else gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
     TRS_CUDA(cudaGetLastError());
     count_launch();
     words->launched = true;

@@ -14,7 +14,7 @@ MAX_RANK, MAX_INPUTS, MAX_OUTPUTS, MAX_INSTRS = 8, 8, 4, 64
 OPS = {"const": 0, "add": 1, "sub": 2, "mul": 3, "div": 4, "neg": 5, "relu": 6, "exp": 7, "relu_vjp": 8,
        "reciprocal": 9, "sqrt": 10, "sin": 11, "cos": 12, "copy": 13, "ne": 14}
 EPILOGUES = {"none": 0, "bias": 1, "bias_relu": 2, "relu": 3, "relu_vjp": 4}
-GEMM_ALGOS = {"auto": 0, "simt_fp32": 1, "tcgen05_3xtf32": 2}
+GEMM_ALGOS = {"auto": 0, "simt_fp32": 1, "tcgen05_3xtf32": 2, "tcgen05_3xtf32_2cta": 3}
 STATUS_NAMES = {0: "ok", 1: "invalid argument", 2: "allocation failed", 3: "CUDA error", 4: "JIT error",
                 5: "unsupported", 6: "no CUDA device", 7: "device status"}
 

@@ -16,7 +16,8 @@ from tests.test_oracle_golden import build_operand
 
 pytestmark = pytest.mark.gpu
 GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
-ALGOS = ["simt_fp32", "tcgen05_3xtf32", "auto"]
+ALGOS = ["simt_fp32", "tcgen05_3xtf32", "tcgen05_3xtf32_2cta", "auto"]
+TC_ALGOS = ["tcgen05_3xtf32", "tcgen05_3xtf32_2cta"]
 
 
 def run(a, b, algo, **kw):
@@ -100,10 +101,12 @@ def test_empty_and_zero_inner():
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 32), (129, 257, 40), (300, 520, 100), (1024, 768, 2048), (64, 64, 4096),
-                                   (1664, 3072, 256), (1700, 3000, 264)])   # 156 tiles on 148 SMs: the split-K tail
-def test_tensor_core_path_odd_shapes_and_k_tails(m, n, k):
+                                   (1664, 3072, 256), (1700, 3000, 264),    # 156 tiles on 148 SMs: the split-K tail
+                                   (2560, 2304, 256), (385, 300, 72)])      # 90 tile pairs on 74 SM pairs; a peer CTA wholly past M
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_tensor_core_path_odd_shapes_and_k_tails(algo, m, n, k):
     a, b = RefTensor.from_numpy(rnd(20, m, k)), RefTensor.from_numpy(rnd(21, k, n, scale=1 / np.sqrt(k)))
-    c, _ = run(a, b, "tcgen05_3xtf32")
+    c, _ = run(a, b, algo)
     ok, worst = matmul_tolerance_ok(c, a.matmul(b).logical(), k)
     assert ok, f"worst error/bound {worst}"
     # tighter than the stated tolerance: the 3-product split keeps ~2^-21 relative accuracy per product
@@ -112,7 +115,8 @@ def test_tensor_core_path_odd_shapes_and_k_tails(m, n, k):
     assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * rms
 
 
-def test_tensor_core_path_keeps_inf_nan_classification():
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_tensor_core_path_keeps_inf_nan_classification(algo):
     # The reference's differential tests classify inf / NaN / sign of matmul results
     # (tests/test_matmul_reference.py:43-50); non-finite operands reroute to the exact-FP32 kernel.
     m, n, k = 128, 256, 64
@@ -121,7 +125,7 @@ def test_tensor_core_path_keeps_inf_nan_classification():
     a[70, 9] = np.nan
     b[9, 200] = -np.inf
     ra, rb = RefTensor.from_numpy(a), RefTensor.from_numpy(b)
-    c, _ = run(ra, rb, "tcgen05_3xtf32")
+    c, _ = run(ra, rb, algo)
     want = ra.matmul(rb).logical()
     assert np.array_equal(np.isnan(c), np.isnan(want))
     assert np.array_equal(np.isinf(c), np.isinf(want))
@@ -130,7 +134,8 @@ def test_tensor_core_path_keeps_inf_nan_classification():
     assert np.allclose(c[finite], want[finite], rtol=1e-4, atol=1e-4)
 
 
-def test_tensor_core_path_with_low_mantissa_bits_all_set():
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_tensor_core_path_with_low_mantissa_bits_all_set(algo):
     # The K-major operand is fed to the MMA unsplit (the MMA drops the low 13 mantissa bits) and only the
     # remainder plane is prepared.  Operands whose low 13 bits are all ones are the worst case for that:
     # if the hardware rounded instead of truncating, every product would be off by about 2^-11.
@@ -139,10 +144,20 @@ def test_tensor_core_path_with_low_mantissa_bits_all_set():
     a = (rng.standard_normal((m, k)).astype(np.float32).view(np.uint32) | np.uint32(0x1FFF)).view(np.float32)
     bt = (rng.standard_normal((n, k)).astype(np.float32).view(np.uint32) | np.uint32(0x1FFF)).view(np.float32)
     ra, rb = RefTensor.from_numpy(a), RefTensor.from_numpy(bt).mT          # both operands K-major
-    c, _ = run(ra, rb, "tcgen05_3xtf32")
+    c, _ = run(ra, rb, algo)
     ref64 = a.astype(np.float64) @ bt.astype(np.float64).T
     rms = np.sqrt(np.mean(ref64 ** 2))
     assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * rms
     # and the same product with a transposed (pre-split) right operand agrees to the same bound
-    c2, _ = run(ra, RefTensor.from_numpy(np.ascontiguousarray(bt.T)), "tcgen05_3xtf32")
+    c2, _ = run(ra, RefTensor.from_numpy(np.ascontiguousarray(bt.T)), algo)
     assert np.abs(c2 - ref64).max() <= 4e-6 * np.sqrt(k) * rms
+
+
+def test_both_tensor_core_kernels_agree_bit_for_bit():
+    # One CTA per 128x256 tile or a CTA pair per 256x256 tile: the same products accumulate in the same
+    # k order, so without a split-K tail the two kernels must produce identical bits.
+    m, n, k = 512, 512, 384
+    a, b = RefTensor.from_numpy(rnd(40, m, k)), RefTensor.from_numpy(rnd(41, k, n, scale=1 / np.sqrt(k)))
+    c1, _ = run(a, b, "tcgen05_3xtf32")
+    c2, _ = run(a, b, "tcgen05_3xtf32_2cta")
+    assert np.array_equal(c1.view(np.uint32), c2.view(np.uint32))
