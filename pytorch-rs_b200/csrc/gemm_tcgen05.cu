@@ -6,15 +6,21 @@
 // hi = tf32(a) and lo = tf32(a - hi); the product uses hi*hi + hi*lo + lo*hi, dropping only the
 // lo*lo term (relative 2^-22), so the result stays within the path's rel 1e-5*sqrt(K) tolerance.
 //
-// Two kernels:
-//   split_tf32_kernel  reads an operand through its (arbitrary) strides once and writes the hi
-//                      and lo planes K-major ([rows, K_pad], K_pad a multiple of 32, zero padded)
-//                      into scratch memory.  Transposed views (.mT operands, the backward GEMMs)
-//                      are handled here, so the GEMM itself sees one layout only.
-//   gemm_tf32x3_kernel one 128x256 output tile per CTA.  Warp 0 drives TMA (no multicast) into a
-//                      2-stage ring of {A_hi, A_lo, B_hi, B_lo} 128-byte-swizzled tiles, warp 1
-//                      issues 12 tcgen05.mma per stage into a 128x256 FP32 accumulator in TMEM,
-//                      warps 2-5 read it back with tcgen05.ld and apply the epilogue.
+// Kernels:
+//   split_tf32_*            prepare the operand planes K-major ([rows, K_pad], K_pad a multiple of 32,
+//                           zero padded) in scratch memory.  A K-major, 16-byte aligned operand is fed
+//                           to the MMA as it lies (the MMA drops the low 13 mantissa bits, i.e. it sees
+//                           hi = truncation) and only its lo plane is written; transposed views (.mT
+//                           operands, the backward GEMMs) are re-laid into hi and lo planes here, so the
+//                           GEMM itself sees one layout only.
+//   gemm_tf32x3_kernel      persistent, one CTA per 128x256 output tile.  Warp 0 drives TMA (no
+//                           multicast) into a 4-stage ring of {A_hi, A_lo, B_hi, B_lo} 64-byte-swizzled
+//                           tiles, warp 1 issues 6 tcgen05.mma per stage into one of two 128x256 FP32
+//                           accumulators in TMEM, warps 2-5 read the other back with tcgen05.ld and
+//                           apply the epilogue.
+//   gemm_tf32x3_pair_kernel the same pipeline on a cluster of two CTAs per 256x256 tile
+//                           (tcgen05.mma.cta_group::2): each CTA stages half of B, which takes the
+//                           shared-memory port off the critical path.  The default where M allows.
 // Every wait on an mbarrier is bounded; on a timeout the kernel records an error word, releases
 // its tensor memory and returns, and the host reports TRS_ERR_DEVICE_STATUS.
 #include <cuda.h>
@@ -71,12 +77,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 
 // K-major operand tile whose rows are one swizzle span (128 or 64 bytes): 8-row groups are
 // 8 * ROW_BYTES apart; layout type 2 = SWIZZLE_128B, 4 = SWIZZLE_64B.
+template <int kRowBytes = ROW_BYTES>
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
-    d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;       // stride between 8-row groups
+    d |= (uint64_t)((8 * kRowBytes) >> 4) << 32;       // stride between 8-row groups
     d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
-    d |= (uint64_t)(ROW_BYTES == 128 ? 2 : (ROW_BYTES == 64 ? 4 : 6)) << 61;
+    d |= (uint64_t)(kRowBytes == 128 ? 2 : (kRowBytes == 64 ? 4 : 6)) << 61;
     return d;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -389,9 +396,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
 //   stage empty  (each CTA)     one multicast tcgen05.commit by the leader's MMA thread
 //   acc full     (each CTA)     one multicast tcgen05.commit by the leader's MMA thread
 //   acc empty    (leader only)  eight arrivals: the four epilogue warps of both CTAs
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_B_TILE_BYTES = (BN / 2) * ROW_BYTES;
-constexpr int PAIR_STAGE_BYTES = 2 * A_TILE_BYTES + 2 * PAIR_B_TILE_BYTES;       // 32 KiB per CTA
+// Measured (TFLOP/s at 4096^3 / 8192^3 / 64 x 1024^3 with bias+relu): 32 floats x 3 stages 277 / 339 / 220,
+// 16 x 6 stages 277 / 336 / 210, 16 x 4 stages 267 / 330 / 203; the one-CTA kernel reaches 259 / 320 / 191.
+constexpr int PAIR_BK = 32;                                                       // 128-byte swizzled rows
+constexpr int PAIR_STAGES = 3;
+constexpr int PAIR_ROW_BYTES = PAIR_BK * 4;
+constexpr int PAIR_A_TILE_BYTES = BM * PAIR_ROW_BYTES;
+constexpr int PAIR_B_TILE_BYTES = (BN / 2) * PAIR_ROW_BYTES;
+constexpr int PAIR_STAGE_BYTES = 2 * PAIR_A_TILE_BYTES + 2 * PAIR_B_TILE_BYTES;  // 64 KiB per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_GROUP_M = 8;                                                   // bands of 8 x 256 rows
 
@@ -445,10 +457,10 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                     const uint32_t full = map_to_cta(smem_u32(&full_bar[s]), 0);
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
-                    tma_load_3d_pair(base, &map_a_hi, full, kb * BK, a_row, batch);
-                    tma_load_3d_pair(base + A_TILE_BYTES, &map_a_lo, full, kb * BK, a_row, batch);
-                    tma_load_3d_pair(base + 2 * A_TILE_BYTES, &map_b_hi, full, kb * BK, b_row, batch);
-                    tma_load_3d_pair(base + 2 * A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, kb * BK, b_row, batch);
+                    tma_load_3d_pair(base, &map_a_hi, full, kb * PAIR_BK, a_row, batch);
+                    tma_load_3d_pair(base + PAIR_A_TILE_BYTES, &map_a_lo, full, kb * PAIR_BK, a_row, batch);
+                    tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES, &map_b_hi, full, kb * PAIR_BK, b_row, batch);
+                    tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, kb * PAIR_BK, b_row, batch);
                 }
             }
             // stay until the leader's last commits have arrived on this CTA's barriers
@@ -475,10 +487,10 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                     if (!mbar_wait(smem_u32(&full_bar[s]), (g / PAIR_STAGES) & 1)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
-                    const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
-                    const uint64_t b_hi = smem_desc(base + 2 * A_TILE_BYTES), b_lo = smem_desc(base + 2 * A_TILE_BYTES + PAIR_B_TILE_BYTES);
+                    const uint64_t a_hi = smem_desc<PAIR_ROW_BYTES>(base), a_lo = smem_desc<PAIR_ROW_BYTES>(base + PAIR_A_TILE_BYTES);
+                    const uint64_t b_hi = smem_desc<PAIR_ROW_BYTES>(base + 2 * PAIR_A_TILE_BYTES), b_lo = smem_desc<PAIR_ROW_BYTES>(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 8; ++k) {
+                    for (int k = 0; k < PAIR_BK / 8; ++k) {
                         const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);
                         umma_tf32_pair(d, a_lo + step, b_hi + step, (kb != kb_begin) || (k != 0));
                         umma_tf32_pair(d, a_hi + step, b_lo + step, 1u);
@@ -669,14 +681,14 @@ EncodeTiledFn encode_tiled() {
 }
 
 int32_t make_operand_map(CUtensorMap* map, const float* base, long long rows, long long k_extent, long long batch,
-                         long long row_stride, long long batch_stride, int box_rows) {
+                         long long row_stride, long long batch_stride, int box_rows, int bk) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[3] = {(cuuint64_t)k_extent, (cuuint64_t)rows, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)batch_stride * 4};
     void* plane = const_cast<float*>(base);
-    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-    const CUtensorMapSwizzle swizzle = ROW_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (ROW_BYTES == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 1};             // rows of bk floats: one swizzle span
+    const CUtensorMapSwizzle swizzle = bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -723,8 +735,8 @@ int32_t device_words(int device, DeviceWords** out) {
     return TRS_OK;
 }
 
-int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long k_pad, long long batch, int box_rows) {
-    return make_operand_map(map, plane, rows, k_pad, batch, k_pad, rows * k_pad, box_rows);
+int32_t make_plane_map(CUtensorMap* map, float* plane, long long rows, long long k_pad, long long batch, int box_rows, int bk) {
+    return make_operand_map(map, plane, rows, k_pad, batch, k_pad, rows * k_pad, box_rows, bk);
 }
 
 // Whether the MMA can read the hi operand straight from the source (K-major, 16-byte aligned
@@ -763,7 +775,7 @@ int32_t launch_split(const float* src, long long batch, long long rows, long lon
 
 // Whether AUTO takes the two-CTA kernel: it pays in 256-row tiles, so it wants at most one eighth
 // of the rows it computes to be padding.
-constexpr bool kPairDefault = false;
+constexpr bool kPairDefault = true;
 
 }  // namespace
 
@@ -801,21 +813,22 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const bool pair = g.algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
     const int b_box = pair ? BN / 2 : BN;                // B^T rows one CTA stages
+    const int bk = pair ? PAIR_BK : BK;                  // floats along K per pipeline stage
     bool a_raw = raw_hi_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
     bool b_raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
-    if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM) != TRS_OK) a_raw = false;
-    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box) != TRS_OK) b_raw = false;
+    if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM, bk) != TRS_OK) a_raw = false;
+    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box, bk) != TRS_OK) b_raw = false;
     TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
     TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
-    if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM));
-    TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM));
-    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box));
-    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box));
+    if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
+    TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
+    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
+    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
     const long long tile_rows = pair ? 2 * BM : BM;
     const long long tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + BN - 1) / BN;
     const long long total_tiles = tiles_m * tiles_n * g.batch;
     if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
-    EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / BK), g.epilogue,
+    EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / bk), g.epilogue,
                    (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles};
     // units that work side by side: SMs, or resident CTA pairs
     const long long units = pair ? words->pair_clusters : sm_count(stream->device);
