@@ -67,6 +67,13 @@ int32_t trsh_contiguous(trsh_tensor t, trsh_tensor* out);
 /* materialising layout ops: try_clone (src/tensor.rs:1517-1575), reshape / view (2032-2189; `view_only`
  * fails instead of copying), PartialEq (286-293) */
 int32_t trsh_clone(trsh_tensor t, trsh_tensor* out);
+/* Memory formats (MemoryFormat, src/memory_format.rs:5-15): 0 preserve_format, 1 contiguous_format,
+ * 2 channels_last (rank 4), 3 channels_last_3d (rank 5).  try_clone_with_memory_format
+ * (src/tensor.rs:1533-1575), try_contiguous (1606-1675; returns the same tensor when the layout already
+ * matches, rejects preserve_format otherwise), is_contiguous_with_memory_format (1004-1014). */
+int32_t trsh_clone_format(trsh_tensor t, int32_t memory_format, trsh_tensor* out);
+int32_t trsh_contiguous_format(trsh_tensor t, int32_t memory_format, trsh_tensor* out);
+int32_t trsh_is_contiguous_format(trsh_tensor t, int32_t memory_format, int32_t* result);
 int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out);
 int32_t trsh_equal(trsh_tensor a, trsh_tensor b, int32_t* result);
 /* squeeze() (all != 0) / squeeze(dim): metadata-only (src/tensor.rs:1305-1336) */
@@ -91,6 +98,10 @@ int32_t trsh_is_grad_enabled(int32_t* on);
  * (unary_output_strides 2751-2766, map_scalar 2718-2727, zip_map 2535-2557 / BroadcastPlan 3601-3693) */
 int32_t trsh_plan_unary(int32_t rank, const int64_t* shape, const int64_t* strides, int64_t* out_strides);
 int32_t trsh_plan_scalar(int32_t rank, const int64_t* shape, const int64_t* strides, int64_t* out_strides);
+/* clone(memory_format) when `for_clone`, else contiguous(memory_format): `copies` = 0 when contiguous() keeps
+ * the tensor's storage, else `out_strides` holds the strides of the packed copy. */
+int32_t trsh_plan_memory_format(int32_t memory_format, int32_t for_clone, int32_t rank, const int64_t* shape, const int64_t* strides,
+                                int32_t* copies, int64_t* out_strides);
 int32_t trsh_plan_binary(int32_t lrank, const int64_t* lshape, const int64_t* lstrides, int32_t rrank,
                          const int64_t* rshape, const int64_t* rstrides, int32_t* out_rank, int64_t* out_shape,
                          int64_t* out_strides);

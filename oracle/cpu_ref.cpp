@@ -38,6 +38,8 @@ enum Status : int {
     MATMUL_RANK = 4,             // TensorError::MatmulRequiresMatrices
     MATMUL_INNER = 5,            // TensorError::MatmulInnerDimensionMismatch
     BAD_OP = 6,
+    FORMAT_RANK = 8,             // TensorError::ContiguousMemoryFormatRankMismatch
+    PRESERVE_UNSUPPORTED = 9,    // TensorError::ContiguousPreserveFormatUnsupported
 };
 
 inline uint32_t bits(float v) { uint32_t b; std::memcpy(&b, &v, 4); return b; }
@@ -698,6 +700,54 @@ int ref_clone_strides(int rank, const i64* shape, const i64* strides, i64* out_s
     std::vector<i64> o;
     if (v.elements() == 0 || is_non_overlapping_and_dense(v.shape, v.strides, v.elements())) o = v.strides;
     else if (int s = elementwise_output_strides(v.shape, {Layout{&v.shape, &v.strides}}, o)) return s;
+    std::copy(o.begin(), o.end(), out_strides);
+    return OK;
+}
+
+// MemoryFormat (memory_format.rs:5-15): 0 preserve, 1 contiguous, 2 channels_last, 3 channels_last_3d.
+// is_contiguous_with_memory_format (tensor.rs:1004-1014, 3717-3724, 3765-3791).
+int ref_is_contiguous_in_format(int format, int rank, const i64* shape, const i64* strides) {
+    View v = make_view(nullptr, 0, rank, shape, strides);
+    if (format <= 1) return layout_is_contiguous(v.shape, v.strides, v.elements()) ? 1 : 0;
+    static const int order4[4] = {1, 3, 2, 0}, order5[5] = {1, 4, 3, 2, 0};
+    const int want = format == 2 ? 4 : 5;
+    const int* order = format == 2 ? order4 : order5;
+    if (rank != want) return 0;
+    bool empty = v.elements() == 0;
+    u64 expected = 1;
+    for (int p = 0; p < want; ++p) {
+        int axis = order[p];
+        if (v.shape[axis] == 1) continue;
+        if ((u64)v.strides[axis] != expected) return 0;
+        unsigned __int128 next = (unsigned __int128)expected * (u64)v.shape[axis];
+        if (next > (unsigned __int128)UINT64_MAX && !empty) return 0;
+        expected = (u64)next;
+    }
+    return 1;
+}
+
+// Strides of try_clone_with_memory_format (tensor.rs:1533-1575) when `for_clone`, else of
+// try_contiguous (1606-1675) when it has to copy.  Returns a Status.
+int ref_memory_format_strides(int format, int for_clone, int rank, const i64* shape, const i64* strides, i64* out_strides) {
+    View v = make_view(nullptr, 0, rank, shape, strides);
+    static const int order4[4] = {1, 3, 2, 0}, order5[5] = {1, 4, 3, 2, 0};
+    const int want = format == 2 ? 4 : (format == 3 ? 5 : -1);
+    std::vector<i64> o;
+    if (want >= 0 && rank != want) {
+        if (for_clone) { if (int s = contiguous_strides(v.shape, o)) return s; }   // preflight (1545-1549)
+        return FORMAT_RANK;
+    }
+    int status = OK;
+    if (format == 0) {
+        if (!for_clone) return PRESERVE_UNSUPPORTED;
+        if (v.elements() == 0 || is_non_overlapping_and_dense(v.shape, v.strides, v.elements())) o = v.strides;
+        else status = elementwise_output_strides(v.shape, {Layout{&v.shape, &v.strides}}, o);
+    } else if (format == 1) {
+        status = contiguous_strides(v.shape, o);
+    } else {
+        status = strides_in_physical_order(v.shape, format == 2 ? order4 : order5, o);
+    }
+    if (status) return status;
     std::copy(o.begin(), o.end(), out_strides);
     return OK;
 }

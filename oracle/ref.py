@@ -25,7 +25,9 @@ UNARY = {"relu": 0, "exp": 1, "neg": 2, "sin": 3, "sqrt": 4, "reciprocal": 5, "c
 BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3}
 SCALAR = {"add": 0, "sub": 1, "mul": 2, "div": 3, "rsub": 4, "rdiv": 5}
 STATUS = {1: "ShapeMismatch", 2: "StrideCalculationOverflow", 3: "ElementCountOverflow",
-          4: "MatmulRequiresMatrices", 5: "MatmulInnerDimensionMismatch", 6: "BadOp"}
+          4: "MatmulRequiresMatrices", 5: "MatmulInnerDimensionMismatch", 6: "BadOp",
+          8: "ContiguousMemoryFormatRankMismatch", 9: "ContiguousPreserveFormatUnsupported"}
+MEMORY_FORMATS = {"preserve_format": 0, "contiguous_format": 1, "channels_last": 2, "channels_last_3d": 3}
 
 
 class RefError(RuntimeError):
@@ -147,9 +149,27 @@ class RefTensor:
                                                 _i64(list(shape)), out)
         return list(out)[:len(shape)] if status == 0 else None
 
-    def clone(self):
-        out = _i64([0] * len(self.shape))
-        _check(lib().ref_clone_strides(len(self.shape), _i64(self.shape), _i64(self.strides), out))
+    def is_contiguous_in(self, memory_format="contiguous_format"):
+        """is_contiguous_with_memory_format (src/tensor.rs:1004-1014)."""
+        return bool(lib().ref_is_contiguous_in_format(MEMORY_FORMATS[memory_format], len(self.shape), _i64(self.shape), _i64(self.strides)))
+
+    def contiguous(self, memory_format="contiguous_format"):
+        """try_contiguous (src/tensor.rs:1606-1675): self when the layout already matches, else a packed copy."""
+        fmt = MEMORY_FORMATS[memory_format]
+        want = {2: 4, 3: 5}.get(fmt)
+        if want is not None and len(self.shape) != want:
+            raise RefError(8)
+        if self.is_contiguous_in(memory_format):
+            return self
+        return self._copy_in_format(fmt, for_clone=0)
+
+    def clone(self, memory_format="preserve_format"):
+        """try_clone_with_memory_format (src/tensor.rs:1533-1575)."""
+        return self._copy_in_format(MEMORY_FORMATS[memory_format], for_clone=1)
+
+    def _copy_in_format(self, fmt, for_clone):
+        out = _i64([0] * max(len(self.shape), 1))
+        _check(lib().ref_memory_format_strides(fmt, for_clone, len(self.shape), _i64(self.shape), _i64(self.strides), out))
         strides = list(out)[:len(self.shape)]
         packed = np.zeros(self.numel, dtype=np.float32)
         if self.numel:

@@ -112,6 +112,22 @@ int32_t trsh_detach(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out
 int32_t trsh_contiguous(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out = wrap(contiguous(get(t))); }); }
 
 int32_t trsh_clone(trsh_tensor t, trsh_tensor* out) { return guarded([&] { *out = wrap(clone(get(t))); }); }
+static MemoryFormat format_arg(int32_t f) {
+    if (f < 0 || f > 3) throw Error(ErrKind::InvalidArgument, "unknown memory format " + std::to_string(f));
+    return (MemoryFormat)f;
+}
+int32_t trsh_clone_format(trsh_tensor t, int32_t memory_format, trsh_tensor* out) {
+    return guarded([&] { *out = wrap(clone(get(t), format_arg(memory_format))); });
+}
+int32_t trsh_contiguous_format(trsh_tensor t, int32_t memory_format, trsh_tensor* out) {
+    return guarded([&] { *out = wrap(contiguous(get(t), format_arg(memory_format))); });
+}
+int32_t trsh_is_contiguous_format(trsh_tensor t, int32_t memory_format, int32_t* result) {
+    return guarded([&] {
+        const Tensor& x = *get(t);
+        *result = is_contiguous_in_format(x.v.shape, x.v.strides, format_arg(memory_format)) ? 1 : 0;
+    });
+}
 int32_t trsh_reshape(trsh_tensor t, int32_t n, const int64_t* shape, int32_t view_only, trsh_tensor* out) {
     return guarded([&] { *out = wrap(reshape(get(t), std::vector<i64>(shape, shape + n), view_only != 0)); });
 }
@@ -153,6 +169,16 @@ int32_t trsh_plan_scalar(int32_t rank, const int64_t* shape, const int64_t* stri
     return guarded([&] {
         Shape o = scalar_output_strides(Shape(shape, shape + rank), Shape(strides, strides + rank));
         std::copy(o.begin(), o.end(), out_strides);
+    });
+}
+int32_t trsh_plan_memory_format(int32_t memory_format, int32_t for_clone, int32_t rank, const int64_t* shape, const int64_t* strides,
+                                int32_t* copies, int64_t* out_strides) {
+    return guarded([&] {
+        Shape o;
+        const bool copy = memory_format_plan(Shape(shape, shape + rank), Shape(strides, strides + rank), format_arg(memory_format),
+                                             for_clone != 0, &o);
+        *copies = copy ? 1 : 0;
+        if (copy) std::copy(o.begin(), o.end(), out_strides);
     });
 }
 int32_t trsh_plan_binary(int32_t lrank, const int64_t* lshape, const int64_t* lstrides, int32_t rrank,

@@ -239,9 +239,12 @@ float item(const Tensor& t) {
     return v;
 }
 
-TensorP contiguous(const TensorP& t) {
-    if (layout_is_contiguous(t->v.shape, t->v.strides)) return t;
-    TensorP out = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, contiguous_strides(t->v.shape), t->device());
+// try_contiguous (src/tensor.rs:1606-1675): the tensor itself when it already has the requested layout,
+// else a packed copy with that format's canonical strides.
+TensorP contiguous(const TensorP& t, MemoryFormat format) {
+    Shape strides;
+    if (!memory_format_plan(t->v.shape, t->v.strides, format, false, &strides)) return t;
+    TensorP out = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, strides, t->device());
     if (t->requires_grad() && grad_enabled()) record(out, GK::Copy, "CloneBackward0", {t.get()}, {}, false);
     return out;
 }

@@ -45,7 +45,12 @@ enum class ErrKind : int {
     ShapeDataMismatch = 21,
     ReshapeInvalid = 22,
     ViewIncompatibleLayout = 23,
+    ContiguousPreserveFormatUnsupported = 24,
+    ContiguousMemoryFormatRankMismatch = 25,
 };
+
+// MemoryFormat (src/memory_format.rs:5-15)
+enum class MemoryFormat : int { Preserve = 0, Contiguous = 1, ChannelsLast = 2, ChannelsLast3d = 3 };
 
 struct Error : std::runtime_error {
     ErrKind kind;
@@ -112,6 +117,11 @@ Shape unary_output_strides(const Shape& shape, const Shape& strides);
 Shape scalar_output_strides(const Shape& shape, const Shape& strides);
 bool reshape_view_strides(const Shape& shape, const Shape& strides, const Shape& new_shape, Shape* out);
 Shape clone_strides(const Shape& shape, const Shape& strides);
+const char* memory_format_name(MemoryFormat f);
+bool is_contiguous_in_format(const Shape& shape, const Shape& strides, MemoryFormat f);
+Shape memory_format_strides(const Shape& shape, MemoryFormat f);
+int memory_format_rank(MemoryFormat f);
+bool memory_format_plan(const Shape& shape, const Shape& strides, MemoryFormat f, bool for_clone, Shape* out);
 void binary_plan(const Shape& lshape, const Shape& lstrides, const Shape& rshape, const Shape& rstrides,
                  Shape* shape, Shape* strides);
 
@@ -135,8 +145,8 @@ TensorP matrix_transpose(const TensorP& t);
 TensorP reverse_dims(const TensorP& t);
 TensorP select0(const TensorP& t, i64 index);
 TensorP detach(const TensorP& t);
-TensorP contiguous(const TensorP& t);
-TensorP clone(const TensorP& t);
+TensorP contiguous(const TensorP& t, MemoryFormat format = MemoryFormat::Contiguous);
+TensorP clone(const TensorP& t, MemoryFormat format = MemoryFormat::Preserve);
 TensorP squeeze(const TensorP& t, i64 dimension);    // INT64_MIN: every singleton dimension
 TensorP reshape(const TensorP& t, const std::vector<i64>& requested, bool view_only);
 bool equal(const TensorP& a, const TensorP& b);

@@ -77,34 +77,51 @@ Shape sorted_output_strides(const Shape& shape, const std::vector<Operand>& ops)
     return out;
 }
 
-bool channels_last_contiguous(const Shape& shape, const Shape& strides) {
-    // src/tensor.rs:3717-3719, 3765-3791 (physical order C, W, H, N)
-    if (shape.size() != 4) return false;
-    static const int order[4] = {1, 3, 2, 0};
+// layout_is_contiguous_in_order (src/tensor.rs:3765-3791): dense when walked in the given physical
+// order (innermost axis first), size-1 axes skipped.
+bool contiguous_in_order(const Shape& shape, const Shape& strides, const int* order, size_t rank) {
+    if (shape.size() != rank) return false;
+    bool empty = false;
+    for (i64 d : shape) empty |= d == 0;
     uint64_t expected = 1;
-    for (int axis : order) {
+    for (size_t pos = 0; pos < rank; ++pos) {
+        const int axis = order[pos];
         if (shape[axis] == 1) continue;
         if ((uint64_t)strides[axis] != expected) return false;
-        expected *= (uint64_t)shape[axis];
+        const __int128 next = (__int128)expected * (uint64_t)shape[axis];
+        if (next > (__int128)UINT64_MAX && !empty) return false;
+        expected = (uint64_t)next;                      // wraps only for empty tensors, as the reference allows
     }
     return true;
 }
 
-Shape channels_last_strides(const Shape& shape) {
-    // src/tensor.rs:4211-4247
-    (void)contiguous_strides(shape);
-    static const int order[4] = {1, 3, 2, 0};
-    Shape out(4, 0);
+const int kChannelsLastOrder[4] = {1, 3, 2, 0};         // physical order C, W, H, N
+const int kChannelsLast3dOrder[5] = {1, 4, 3, 2, 0};    // C, W, H, D, N
+
+bool channels_last_contiguous(const Shape& shape, const Shape& strides) {
+    // src/tensor.rs:3717-3719
+    return contiguous_in_order(shape, strides, kChannelsLastOrder, 4);
+}
+
+// strides_in_physical_order (src/tensor.rs:4225-4247): a zero-sized physical dimension zeroes every later stride.
+Shape strides_in_order(const Shape& shape, const int* order, size_t rank) {
+    (void)contiguous_strides(shape);                     // the canonical strides must be representable too
+    Shape out(rank, 0);
     i64 stride = 1;
-    for (int pos = 0; pos < 4; ++pos) {
+    for (size_t pos = 0; pos < rank; ++pos) {
         out[order[pos]] = stride;
-        if (pos < 3) {
+        if (pos + 1 < rank) {
             __int128 p = (__int128)stride * shape[order[pos]];
             if (p > (__int128)INT64_MAX) throw Error(ErrKind::StrideCalculationOverflow, "Stride calculation overflowed");
             stride = (i64)p;
         }
     }
     return out;
+}
+
+Shape channels_last_strides(const Shape& shape) {
+    // src/tensor.rs:4211-4216
+    return strides_in_order(shape, kChannelsLastOrder, 4);
 }
 
 }  // namespace
@@ -199,6 +216,57 @@ bool reshape_view_strides(const Shape& shape, const Shape& strides, const Shape&
 Shape clone_strides(const Shape& shape, const Shape& strides) {
     if (is_non_overlapping_and_dense(shape, strides)) return strides;
     return sorted_output_strides(shape, {Operand{&shape, &strides}});
+}
+
+const char* memory_format_name(MemoryFormat f) {
+    // Display for MemoryFormat (src/memory_format.rs:17-26)
+    switch (f) {
+        case MemoryFormat::Preserve: return "preserve_format";
+        case MemoryFormat::Contiguous: return "contiguous_format";
+        case MemoryFormat::ChannelsLast: return "channels_last";
+        default: return "channels_last_3d";
+    }
+}
+
+// is_contiguous_with_memory_format (src/tensor.rs:1004-1014): preserve queries like contiguous.
+bool is_contiguous_in_format(const Shape& shape, const Shape& strides, MemoryFormat f) {
+    switch (f) {
+        case MemoryFormat::Preserve:
+        case MemoryFormat::Contiguous: return layout_is_contiguous(shape, strides);
+        case MemoryFormat::ChannelsLast: return contiguous_in_order(shape, strides, kChannelsLastOrder, 4);
+        default: return contiguous_in_order(shape, strides, kChannelsLast3dOrder, 5);
+    }
+}
+
+// Canonical strides of an explicit format (src/tensor.rs:1566-1568, 1659-1661); the caller has checked the rank.
+Shape memory_format_strides(const Shape& shape, MemoryFormat f) {
+    if (f == MemoryFormat::ChannelsLast) return strides_in_order(shape, kChannelsLastOrder, 4);
+    if (f == MemoryFormat::ChannelsLast3d) return strides_in_order(shape, kChannelsLast3dOrder, 5);
+    return contiguous_strides(shape);
+}
+
+// The rank a channel-last format needs, or -1 (src/tensor.rs:1539-1543).
+int memory_format_rank(MemoryFormat f) {
+    return f == MemoryFormat::ChannelsLast ? 4 : (f == MemoryFormat::ChannelsLast3d ? 5 : -1);
+}
+
+// Layout decision of clone(memory_format) (src/tensor.rs:1533-1575) and of contiguous(memory_format)
+// (1606-1675).  Returns false when contiguous() keeps the tensor's own storage; otherwise `out`
+// holds the strides of the packed copy.
+bool memory_format_plan(const Shape& shape, const Shape& strides, MemoryFormat f, bool for_clone, Shape* out) {
+    const int want = memory_format_rank(f);
+    if (want >= 0 && (int)shape.size() != want) {
+        if (for_clone) (void)contiguous_strides(shape);        // clone validates the destination metadata first (1545-1549)
+        throw Error(ErrKind::ContiguousMemoryFormatRankMismatch,
+                    "required rank " + std::to_string(want) + " tensor to use " + memory_format_name(f) + " format");
+    }
+    if (!for_clone) {
+        if (is_contiguous_in_format(shape, strides, f)) return false;
+        if (f == MemoryFormat::Preserve)
+            throw Error(ErrKind::ContiguousPreserveFormatUnsupported, "preserve memory format is unsupported by the contiguous operator");
+    }
+    *out = f == MemoryFormat::Preserve ? clone_strides(shape, strides) : memory_format_strides(shape, f);
+    return true;
 }
 
 static std::string shape_text(const Shape& s) {

@@ -166,10 +166,12 @@ TensorP matmul(const TensorP& l, const TensorP& r) {
     return out;
 }
 
-// try_clone (src/tensor.rs:1517-1575): an independent copy; dense layouts keep their strides,
-// other views are packed in the same dimension order; offset 0.
-TensorP clone(const TensorP& t) {
-    const Shape strides = clone_strides(t->v.shape, t->v.strides);
+// try_clone_with_memory_format (src/tensor.rs:1517-1575): an independent copy at offset 0.  Preserve
+// keeps dense strides and packs other views in the same dimension order; the explicit formats lay
+// the copy out row-major or channel-last.
+TensorP clone(const TensorP& t, MemoryFormat format) {
+    Shape strides;
+    memory_format_plan(t->v.shape, t->v.strides, format, true, &strides);
     TensorP out = pointwise_node(TRS_OP_COPY, 0.f, {t->v}, t->v.shape, strides, t->device());
     if (t->requires_grad() && grad_enabled()) record(out, GK::Copy, "CloneBackward0", {t.get()}, {}, false);
     return out;

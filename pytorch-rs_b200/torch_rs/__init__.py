@@ -15,7 +15,8 @@ import ctypes
 import numpy as np
 
 from . import _abi, _device, _host  # noqa: F401
-from .tensor import Tensor, device, _device_index, _wrap
+from .tensor import (Tensor, device, _device_index, _wrap, memory_format, preserve_format, contiguous_format,  # noqa: F401
+                     channels_last, channels_last_3d)
 
 float32 = "torch.float32"
 
@@ -84,8 +85,8 @@ def reshape(input, shape):
     return _tensor_arg(input, "reshape").reshape(*shape)
 
 
-def clone(input):
-    return _tensor_arg(input, "clone").clone()
+def clone(input, *, memory_format=None):
+    return _tensor_arg(input, "clone").clone(memory_format=memory_format)
 
 
 def _tensor_arg(value, name):

@@ -38,6 +38,9 @@ _PROTOTYPES = {
     "trsh_detach": [H, HP],
     "trsh_contiguous": [H, HP],
     "trsh_clone": [H, HP],
+    "trsh_clone_format": [H, ctypes.c_int32, HP],
+    "trsh_contiguous_format": [H, ctypes.c_int32, HP],
+    "trsh_is_contiguous_format": [H, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)],
     "trsh_reshape": [H, ctypes.c_int32, I64P, ctypes.c_int32, HP],
     "trsh_equal": [H, H, I32P],
     "trsh_squeeze": [H, ctypes.c_int32, ctypes.c_int64, HP],
@@ -53,6 +56,7 @@ _PROTOTYPES = {
     "trsh_is_grad_enabled": [I32P],
     "trsh_plan_unary": [ctypes.c_int32, I64P, I64P, I64P],
     "trsh_plan_scalar": [ctypes.c_int32, I64P, I64P, I64P],
+    "trsh_plan_memory_format": [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, I64P, I64P, I32P, I64P],
     "trsh_plan_binary": [ctypes.c_int32, I64P, I64P, ctypes.c_int32, I64P, I64P, I32P, I64P, I64P],
     "trsh_materialize": [H],
     "trsh_sync": [ctypes.c_int32],

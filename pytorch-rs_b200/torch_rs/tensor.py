@@ -52,6 +52,41 @@ class device:
         return hash((self.type, self.index))
 
 
+class memory_format:
+    """Memory-format descriptor (reference: PyMemoryFormat, src/python_memory_format.rs:14-52): four
+    canonical instances, printed as ``torch.<name>``, compared by identity of the format."""
+    _names = ("preserve_format", "contiguous_format", "channels_last", "channels_last_3d")
+
+    def __init__(self, code: int):
+        self._code = int(code)
+
+    def __repr__(self):
+        return "torch." + self._names[self._code]
+
+    __str__ = __repr__
+
+    def __eq__(self, other):
+        return isinstance(other, memory_format) and other._code == self._code
+
+    def __hash__(self):
+        return hash(("memory_format", self._code))
+
+    def __reduce__(self):
+        return repr(self)
+
+
+preserve_format = memory_format(0)
+contiguous_format = memory_format(1)
+channels_last = memory_format(2)
+channels_last_3d = memory_format(3)
+
+
+def _memory_format_code(value, op="contiguous") -> int:
+    if not isinstance(value, memory_format):
+        raise TypeError(f"{op}(): argument 'memory_format' must be torch.memory_format, not {type(value).__name__}")
+    return value._code
+
+
 def _device_index(dev) -> int:
     if dev is None:
         raise RuntimeError("pass device='cuda' (or 'cuda:N'): tensors without a CUDA device belong to the "
@@ -143,8 +178,13 @@ class Tensor:
     def is_leaf(self):
         return self._flags()[1]
 
-    def is_contiguous(self):
-        return self._flags()[2]
+    def is_contiguous(self, memory_format=None):
+        """is_contiguous_with_memory_format (src/tensor.rs:1004-1014); preserve_format queries like contiguous_format."""
+        if memory_format is None:
+            return self._flags()[2]
+        result = ctypes.c_int32()
+        _host.check(_host.lib().trsh_is_contiguous_format(self._h, _memory_format_code(memory_format, "is_contiguous"), ctypes.byref(result)))
+        return bool(result.value)
 
     def is_pending(self):
         """True while this tensor's values are still a recorded, not yet executed, pointwise chain."""
@@ -259,11 +299,17 @@ class Tensor:
     def detach(self):
         return self._view(_host.lib().trsh_detach)
 
-    def contiguous(self):
-        return self._view(_host.lib().trsh_contiguous)
+    def contiguous(self, memory_format=None):
+        """try_contiguous (src/tensor.rs:1606-1675): self's storage when the layout already matches the format."""
+        if memory_format is None:
+            return self._view(_host.lib().trsh_contiguous)
+        return self._view(_host.lib().trsh_contiguous_format, _memory_format_code(memory_format))
 
-    def clone(self):
-        return self._view(_host.lib().trsh_clone)
+    def clone(self, memory_format=None):
+        """try_clone_with_memory_format (src/tensor.rs:1533-1575); the default is preserve_format."""
+        if memory_format is None:
+            return self._view(_host.lib().trsh_clone)
+        return self._view(_host.lib().trsh_clone_format, _memory_format_code(memory_format, "clone"))
 
     def _reshape(self, shape, view_only):
         if len(shape) == 1 and isinstance(shape[0], (tuple, list)):

@@ -120,3 +120,55 @@ def test_layout_planner_extreme_empty_goldens():
         assert list(out)[:n] == case["scalar_expected"]
         if "unary_error" in case:
             assert lib.trsh_plan_unary(n, _arr(case["shape"]), _arr(case["strides"]), out) == 11      # StrideCalculationOverflow
+
+
+def test_memory_format_planner_matches_the_checker_and_the_reference_goldens():
+    """clone(memory_format) / contiguous(memory_format) layout decisions: random rank-4/5 views against the
+    CPU checker, plus the stride goldens of tests/tensor_baseline.rs:2476-2610, 2698-2770."""
+    import json
+    import os
+    import numpy as np
+    from oracle import ref
+    lib = _host.lib()
+
+    def plan(fmt, for_clone, shape, strides):
+        out, copies = _arr([0] * max(len(shape), 1)), ctypes.c_int32()
+        status = lib.trsh_plan_memory_format(fmt, for_clone, len(shape), _arr(shape), _arr(strides), ctypes.byref(copies), out)
+        return status, bool(copies.value), list(out)[:len(shape)]
+
+    rng = np.random.default_rng(321)
+    for _ in range(2000):
+        rank = int(rng.choice([3, 4, 5]))
+        base = [int(rng.choice([0, 1, 1, 2, 3, 4])) if rng.random() < 0.9 else 1 for _ in range(rank)]
+        strides, s = [0] * rank, 1
+        for axis in range(rank - 1, -1, -1):
+            step = int(rng.choice([1, 1, 1, 2]))
+            strides[axis] = s * step
+            s *= max(base[axis], 1) * step
+        perm = list(rng.permutation(rank))
+        shape, strides = [base[p] for p in perm], [strides[p] for p in perm]
+        for name, fmt in ref.MEMORY_FORMATS.items():
+            for for_clone in (1, 0):
+                want = (ctypes.c_int64 * max(rank, 1))()
+                want_status = ref.lib().ref_memory_format_strides(fmt, for_clone, rank, _arr(shape), _arr(strides), want)
+                shares = (not for_clone) and want_status in (0, 9) and (fmt < 2 or rank == {2: 4, 3: 5}[fmt]) and bool(
+                    ref.lib().ref_is_contiguous_in_format(fmt, rank, _arr(shape), _arr(strides)))
+                status, copies, got = plan(fmt, for_clone, shape, strides)
+                if shares:
+                    assert status == 0 and not copies, (name, shape, strides)
+                elif want_status == 0:
+                    assert status == 0 and copies and got == list(want)[:rank], (name, for_clone, shape, strides)
+                else:
+                    assert status == {8: 25, 9: 24, 2: 11}[want_status], (name, for_clone, shape, strides, status, want_status)
+
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))["memory_format"]["contiguous"]
+    for case in gold["empty_cases"]:
+        shape = case["shape"]
+        assert plan(2, 0, shape, ref.contiguous_strides(shape)) == (0, True, case["expected"])
+    shape = gold["empty_volume"]["shape"]
+    assert plan(3, 0, shape, ref.contiguous_strides(shape)) == (0, True, gold["empty_volume"]["expected"])
+    assert plan(2, 0, gold["singleton"]["shape"], gold["singleton"]["strides"])[:2] == (0, False)
+    assert plan(2, 0, gold["arange_shape"], [12, 4, 2, 1]) == (0, True, gold["channels_last_strides"])
+    assert plan(3, 1, [1, 2, 3, 4], [24, 12, 4, 1])[0] == 25          # ContiguousMemoryFormatRankMismatch
+    assert "required rank 5 tensor to use channels_last_3d format" in lib.trsh_last_error().decode()
+    assert plan(0, 0, [2, 3], [1, 2])[0] == 24                       # ContiguousPreserveFormatUnsupported

@@ -132,3 +132,135 @@ def test_squeeze_and_unbind_views_and_their_gradients():
     want = np.zeros((3, 4), dtype=np.float32)
     want[0], want[2] = 2.0, 1.0
     assert np.array_equal(w.grad.numpy(), want)
+
+
+# ---- memory formats: clone / contiguous / is_contiguous with channels_last and channels_last_3d ---------------
+
+FORMATS = {"preserve_format": torch.preserve_format, "contiguous_format": torch.contiguous_format,
+           "channels_last": torch.channels_last, "channels_last_3d": torch.channels_last_3d}
+
+
+def _bits(values):
+    return np.array([int(h, 16) for h in values], dtype=np.uint32).view(np.float32)
+
+
+def _format_source(case, patterns):
+    values = _bits([patterns[i % len(patterns)] for i in range(case["count"])])
+    if "outer_shape" in case:
+        return torch.tensor(values.reshape(case["outer_shape"]), device=DEV)[case["select0"]]
+    t = torch.tensor(values.reshape(case["shape"]), device=DEV)
+    return t.transpose(*case["transpose"]) if "transpose" in case else t
+
+
+def test_reference_goldens_for_channel_last_clones():
+    m = GOLD["memory_format"]
+    for key, fmt in (("clone_channels_last", "channels_last"), ("clone_channels_last_3d", "channels_last_3d")):
+        for case in m[key]["cases"]:
+            src = _format_source(case, m["bit_patterns"])
+            out = src.clone(memory_format=FORMATS[fmt])
+            assert list(out.stride()) == case["expected_strides"], (key, case["name"])
+            assert out.shape == src.shape and out.storage_offset() == 0
+            assert out.is_contiguous(memory_format=FORMATS[fmt]) and not out.shares_storage_with(src)
+            # a copy moves bits: signed zeros, denormals, infinities and NaN payloads survive
+            assert np.array_equal(out.numpy().view(np.uint32), src.numpy().view(np.uint32))
+    err = m["clone_channels_last_3d"]["rank_error"]
+    with pytest.raises(RuntimeError, match=err["message"]):
+        torch.zeros(*err["shape"], device=DEV).clone(memory_format=torch.channels_last_3d)
+
+
+def test_reference_goldens_for_contiguous_with_memory_format():
+    c = GOLD["memory_format"]["contiguous"]
+    src = torch.tensor(np.arange(24, dtype=np.float32).reshape(c["arange_shape"]), device=DEV)
+    cl = src.contiguous(memory_format=torch.channels_last)
+    assert list(cl.stride()) == c["channels_last_strides"] and cl.storage_offset() == 0
+    assert cl.is_contiguous(memory_format=torch.channels_last) and not cl.is_contiguous() and not cl.shares_storage_with(src)
+    assert cl.numpy().reshape(-1).tolist() == list(range(24))
+    assert cl.contiguous(memory_format=torch.channels_last).shares_storage_with(cl)
+    cloned = cl.clone()
+    assert list(cloned.stride()) == c["channels_last_strides"] and not cloned.shares_storage_with(cl)
+    row_major = cl.contiguous(memory_format=torch.contiguous_format)
+    assert list(row_major.stride()) == c["row_major_strides"] and not row_major.shares_storage_with(cl)
+    assert row_major.numpy().reshape(-1).tolist() == list(range(24))
+    assert list((cl + 1.0).stride()) == c["add_scalar_strides"]
+    assert cl.sum().item() == c["sum"]
+    vol = torch.tensor(np.arange(48, dtype=np.float32).reshape(c["volume_shape"]), device=DEV)
+    v3 = vol.contiguous(memory_format=torch.channels_last_3d)
+    assert list(v3.stride()) == c["channels_last_3d_strides"] and v3.is_contiguous(memory_format=torch.channels_last_3d)
+    assert v3.numpy().reshape(-1).tolist() == list(range(48)) and not v3.shares_storage_with(vol)
+    single = torch.zeros(*c["singleton"]["shape"], device=DEV)
+    kept = single.contiguous(memory_format=torch.channels_last)
+    assert kept.shares_storage_with(single) and list(kept.stride()) == c["singleton"]["strides"]
+    for case in c["empty_cases"]:
+        out = torch.zeros(*case["shape"], device=DEV).contiguous(memory_format=torch.channels_last)
+        assert list(out.stride()) == case["expected"] and out.is_contiguous(memory_format=torch.channels_last)
+    out = torch.zeros(*c["empty_volume"]["shape"], device=DEV).contiguous(memory_format=torch.channels_last_3d)
+    assert list(out.stride()) == c["empty_volume"]["expected"]
+    with pytest.raises(RuntimeError, match=c["rank_error_message"]):
+        torch.zeros(2, 3, device=DEV).contiguous(memory_format=torch.channels_last)
+    with pytest.raises(RuntimeError, match="preserve memory format is unsupported by the contiguous operator"):
+        src.mT.contiguous(memory_format=torch.preserve_format)
+    with pytest.raises(TypeError, match="must be torch.memory_format, not str"):
+        src.contiguous(memory_format="channels_last")
+
+
+def test_memory_format_queries_match_reference_goldens():
+    for case in GOLD["memory_format"]["queries"]["cases"]:
+        count = int(np.prod(case["shape"]))
+        # rebuild the strided view from a permutation of a contiguous tensor: order axes by descending stride
+        order = sorted(range(len(case["shape"])), key=lambda a: (-case["strides"][a], a))
+        base = torch.zeros(*[case["shape"][a] for a in order], device=DEV)
+        inverse = [order.index(a) for a in range(len(order))]
+        view = base.permute(*inverse)
+        if count:                                              # for empty tensors the strides are not unique
+            assert list(view.stride()) == case["strides"]
+            for name, fmt in FORMATS.items():
+                if name in case:
+                    assert view.is_contiguous(memory_format=fmt) == case[name], (case, name)
+
+
+def test_channel_last_clone_gradients_are_identity():
+    for case in GOLD["memory_format"]["autograd_clone"]["cases"]:
+        n = int(np.prod(case["shape"]))
+        leaf = torch.tensor(np.arange(1, n + 1, dtype=np.float32).reshape(case["shape"]), device=DEV, requires_grad=True)
+        src = leaf.transpose(*case["transpose"])
+        cloned = src.clone(memory_format=FORMATS[case["format"]])
+        assert list(cloned.stride()) == case["strides"] and cloned.requires_grad and not cloned.is_leaf
+        del src
+        cloned.sum().backward()
+        assert np.array_equal(leaf.grad.numpy(), np.full(case["shape"], case["grad"], dtype=np.float32))
+        with torch.no_grad():
+            quiet = leaf.transpose(*case["transpose"]).clone(memory_format=FORMATS[case["format"]])
+        assert list(quiet.stride()) == case["strides"] and not quiet.requires_grad and quiet.is_leaf
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_memory_format_copies_match_the_checker(seed):
+    rng = np.random.default_rng(100 + seed)
+    rank = 4 if seed % 2 == 0 else 5
+    shape = [int(d) for d in rng.integers(1, 7, rank)]
+    base = rnd(seed, *shape)
+    perm = [int(p) for p in rng.permutation(rank)]
+    t, r = torch.tensor(base, device=DEV).permute(*perm), RefTensor.from_numpy(base).permute(perm)
+    fmt = "channels_last" if rank == 4 else "channels_last_3d"
+    for name in ("preserve_format", "contiguous_format", fmt):
+        got, want = t.clone(memory_format=FORMATS[name]), r.clone(name)
+        assert list(got.stride()) == want.strides, (name, shape, perm)
+        assert np.array_equal(got.numpy().view(np.uint32), want.logical().view(np.uint32))
+        assert t.is_contiguous(memory_format=FORMATS[name]) == r.is_contiguous_in(name)
+    for name in ("contiguous_format", fmt):
+        got, want = t.contiguous(memory_format=FORMATS[name]), r.contiguous(name)
+        assert list(got.stride()) == want.strides and got.shares_storage_with(t) == (want is r)
+        assert np.array_equal(got.numpy().view(np.uint32), want.logical().view(np.uint32))
+        # ops on the copy keep its layout (channel-last precedence of the output-stride rule)
+        assert list(got.relu().stride()) == want.relu().strides
+
+
+def test_channels_last_copy_of_a_large_tensor_runs_at_memory_speed_layout():
+    # [N, C, H, W] = [8, 64, 56, 56] -> channel-last and back; both directions transpose C against H*W
+    x = rnd(7, 8, 64, 56, 56)
+    t = torch.tensor(x, device=DEV)
+    cl = t.contiguous(memory_format=torch.channels_last)
+    assert list(cl.stride()) == [64 * 56 * 56, 1, 56 * 64, 64]
+    assert np.array_equal(cl.numpy(), x)
+    back = cl.contiguous()
+    assert back.is_contiguous() and np.array_equal(back.numpy(), x)

@@ -263,3 +263,52 @@ def test_strided_relu_gradients_golden_by_composition():
     g_strided = strided.relu_vjp(upstream)                                               # logical [4,3]
     grad[1] += ref.permute_vjp(g_strided, [3, 4], [1, 0])                                # transpose VJP
     assert grad.reshape(-1).tolist() == [float(v) for v in g["expected_grad"]]
+
+
+def _memory_format_source(case, patterns):
+    """Builds the source views of the reference's channel-last clone tests from their recipe."""
+    values = f32_from_hex([patterns[i % len(patterns)] for i in range(case["count"])])
+    if "outer_shape" in case:
+        return RefTensor(values, case["outer_shape"]).select0(case["select0"])
+    t = RefTensor(values, case["shape"])
+    return t.transpose(*case["transpose"]) if "transpose" in case else t
+
+
+def test_memory_format_goldens():
+    m = GOLD["memory_format"]
+    for case in m["queries"]["cases"]:
+        t = RefTensor(np.zeros(max(int(np.prod(case["shape"])), 0), dtype=np.float32), case["shape"], case["strides"])
+        for fmt in ref.MEMORY_FORMATS:
+            if fmt in case:
+                assert t.is_contiguous_in(fmt) == case[fmt], (case, fmt)
+    for key, fmt in (("clone_channels_last", "channels_last"), ("clone_channels_last_3d", "channels_last_3d")):
+        for case in m[key]["cases"]:
+            src = _memory_format_source(case, m["bit_patterns"])
+            out = src.clone(fmt)
+            assert out.strides == case["expected_strides"], case["name"]
+            assert out.is_contiguous_in(fmt) and out.shape == src.shape
+            assert np.array_equal(out.logical().view(np.uint32), src.logical().view(np.uint32))   # NaN payloads survive a copy
+    with pytest.raises(ref.RefError) as err:
+        RefTensor(np.zeros(24, dtype=np.float32), m["clone_channels_last_3d"]["rank_error"]["shape"]).clone("channels_last_3d")
+    assert err.value.kind == m["clone_channels_last_3d"]["rank_error"]["kind"]
+
+    c = m["contiguous"]
+    src = RefTensor(np.arange(24, dtype=np.float32), c["arange_shape"])
+    cl = src.contiguous("channels_last")
+    assert cl.strides == c["channels_last_strides"] and not cl.is_contiguous_in() and cl.is_contiguous_in("channels_last")
+    assert cl.logical().reshape(-1).tolist() == src.logical().reshape(-1).tolist()
+    assert cl.contiguous("channels_last") is cl                    # matching layout: storage is shared
+    assert cl.clone().strides == c["channels_last_strides"]
+    assert cl.contiguous().strides == c["row_major_strides"]
+    assert (cl + 1.0).strides == c["add_scalar_strides"]
+    assert float(cl.sum()) == c["sum"]
+    vol = RefTensor(np.arange(48, dtype=np.float32), c["volume_shape"]).contiguous("channels_last_3d")
+    assert vol.strides == c["channels_last_3d_strides"]
+    single = RefTensor(np.zeros(40, dtype=np.float32), c["singleton"]["shape"])
+    assert single.contiguous("channels_last") is single and single.strides == c["singleton"]["strides"]
+    for case in c["empty_cases"]:
+        assert RefTensor(np.zeros(0, dtype=np.float32), case["shape"]).contiguous("channels_last").strides == case["expected"]
+    assert RefTensor(np.zeros(0, dtype=np.float32), c["empty_volume"]["shape"]).contiguous("channels_last_3d").strides == c["empty_volume"]["expected"]
+    with pytest.raises(ref.RefError) as err:
+        cl.mT.contiguous("preserve_format")
+    assert err.value.kind == "ContiguousPreserveFormatUnsupported"
