@@ -253,7 +253,7 @@ def run_ours(args, rank, world, local_rank):
     x_host[...] = xs
     b_host[...] = b
 
-    E2E_SLABS = 8                                  # physical-row slabs: upload of slab i+1 overlaps read-back of slab i
+    E2E_SLABS = args.e2e_slabs                     # physical-row slabs: upload of slab i+1 overlaps read-back of slab i
 
     def step_e2e():
         rows = N_SIDE // E2E_SLABS
@@ -473,6 +473,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-slabs", type=int, default=8, help="row slabs per end-to-end step (must divide 8192)")
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "t1", "c3", "c4", "c5"],
                     help="c2 (default) is the headline fused chain; the others are BASELINE's remaining configs")
     ap.add_argument("--no-extra", action="store_true", help="skip the relu(x+y) and matmul side figures")

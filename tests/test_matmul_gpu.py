@@ -132,6 +132,10 @@ def test_tensor_core_path_keeps_inf_nan_classification(algo):
     finite = np.isfinite(want)
     assert np.array_equal(np.sign(c[np.isinf(want)]), np.sign(want[np.isinf(want)]))
     assert np.allclose(c[finite], want[finite], rtol=1e-4, atol=1e-4)
+    # both operands K-major (the right one through .mT): both are fed to the MMA as they lie in memory
+    c2, _ = run(ra, RefTensor.from_numpy(np.ascontiguousarray(b.T)).mT, algo)
+    assert np.array_equal(np.isnan(c2), np.isnan(want)) and np.array_equal(np.isinf(c2), np.isinf(want))
+    assert np.allclose(c2[finite], want[finite], rtol=1e-4, atol=1e-4)
 
 
 @pytest.mark.parametrize("algo", TC_ALGOS)
@@ -161,3 +165,18 @@ def test_both_tensor_core_kernels_agree_bit_for_bit():
     c1, _ = run(a, b, "tcgen05_3xtf32")
     c2, _ = run(a, b, "tcgen05_3xtf32_2cta")
     assert np.array_equal(c1.view(np.uint32), c2.view(np.uint32))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 32), (512, 768, 1024), (300, 500, 200), (2560, 2304, 288), (4, 1000, 96)])
+def test_pair_kernel_with_two_k_major_operands(m, n, k):
+    # A @ W.mT with both operands K-major: both are fed to the MMA as they lie in memory, only lo planes are prepared.
+    a, wt = RefTensor.from_numpy(rnd(50, m, k)), RefTensor.from_numpy(rnd(51, n, k, scale=1 / np.sqrt(k)))
+    c, _ = run(a, wt.mT, "tcgen05_3xtf32_2cta")
+    ref64 = a.logical().astype(np.float64) @ wt.logical().astype(np.float64).T
+    rms = np.sqrt(np.mean(ref64 ** 2))
+    assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * rms
+    # the one-CTA kernel accumulates the same products in the same order: identical bits unless the pair
+    # kernel cut its last round of tiles in two along K
+    c1, _ = run(a, wt.mT, "tcgen05_3xtf32")
+    if (m, n, k) != (2560, 2304, 288):
+        assert np.array_equal(c.view(np.uint32), c1.view(np.uint32))
