@@ -135,8 +135,19 @@ int32_t trs_pointwise(const trs_program* program, const trs_operand* inputs, con
     JitEntry* entry = nullptr;
     TRS_TRY(get_kernel(pw_generate_source(program, plan), true, &entry));
     void* args[] = {&plan.params};
-    TRS_CUDA(cudaLaunchKernel((const void*)entry->kernel, dim3((unsigned)plan.grid), dim3(plan.block), args, 0,
-                              stream->stream));
+    // Programmatic dependent launch: the kernel starts with griddepcontrol.wait, so its blocks may be
+    // scheduled while the stream's previous kernel drains (hides the launch gap between chained kernels).
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)plan.grid);
+    cfg.blockDim = dim3(plan.block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream->stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    TRS_CUDA(cudaLaunchKernelExC(&cfg, (const void*)entry->kernel, args));
     count_launch();
     return TRS_OK;
 }

@@ -330,6 +330,11 @@ void emit_chain(std::ostringstream& s, const trs_program* prog) {
 const char* kVectorKernel = R"SRC(
 // Vector class: one work item = 4 consecutive elements of the innermost output dim.
 extern "C" __global__ void __launch_bounds__(BLOCK) trs_pw(const Params p) {
+    // Launched with programmatic stream serialization: blocks of this grid become resident while the
+    // previous kernel of the stream drains.  Nothing is read or written before that kernel has completed
+    // and flushed; after that the next kernel's blocks may take the slots this grid frees.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     float xin[UNROLL][NIN > 0 ? NIN : 1][4];
     ofs_t ooff[UNROLL][NOUT];
     u32 nvalid[UNROLL];
@@ -416,6 +421,11 @@ const char* kTiledKernel = R"SRC(
 // TDIM into padded shared memory and consumed along dim 0; everything else is accessed along
 // dim 0 directly, so every global access of the hot operands is coalesced.
 extern "C" __global__ void __launch_bounds__(256) trs_pw(const Params p) {
+    // Launched with programmatic stream serialization: blocks of this grid become resident while the
+    // previous kernel of the stream drains.  Nothing is read or written before that kernel has completed
+    // and flushed; after that the next kernel's blocks may take the slots this grid frees.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     __shared__ float tile[NTRANS > 0 ? NTRANS : 1][32][33];
     u64 cta = blockIdx.x;
     const u32 t0 = (u32)(cta % p.aux[0]); cta /= p.aux[0];
@@ -478,6 +488,11 @@ const char* kTiledVecKernel = R"SRC(
 // Tiled class, 128-bit variant: 64x64 tiles.  Staged inputs are read with float4 along TDIM
 // (their unit-stride axis) into padded shared memory; everything else moves as float4 along dim 0.
 extern "C" __global__ void __launch_bounds__(256) trs_pw(const Params p) {
+    // Launched with programmatic stream serialization: blocks of this grid become resident while the
+    // previous kernel of the stream drains.  Nothing is read or written before that kernel has completed
+    // and flushed; after that the next kernel's blocks may take the slots this grid frees.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     __shared__ float tile[NTRANS > 0 ? NTRANS : 1][64][65];
     u64 cta = blockIdx.x;
     const u32 t0 = (u32)(cta % p.aux[0]); cta /= p.aux[0];
