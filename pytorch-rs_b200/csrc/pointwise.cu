@@ -18,7 +18,7 @@ struct JitEntry {
     std::string cubin;
 };
 std::mutex g_jit_mu;
-std::unordered_map<std::string, JitEntry> g_jit_cache;   // key: generated source text
+std::unordered_map<std::string, JitEntry> g_jit_cache;   // key: pw_cache_key (what the generated source depends on)
 
 int32_t compile_cubin(const std::string& source, std::string* cubin) {
     nvrtcProgram prog;
@@ -46,14 +46,15 @@ int32_t compile_cubin(const std::string& source, std::string* cubin) {
     return TRS_OK;
 }
 
-// Returns the cache entry for `source`, compiling it if needed; loads it onto the GPU when
-// `load` is set (loading needs a device, compiling does not).
-int32_t get_kernel(const std::string& source, bool load, JitEntry** out) {
+// Returns the cache entry of this chain and plan, generating and compiling its source if needed; loads
+// it onto the GPU when `load` is set (loading needs a device, compiling does not).
+int32_t get_kernel(const trs_program* program, const PwPlan& plan, bool load, JitEntry** out) {
+    const std::string key = pw_cache_key(program, plan);
     std::lock_guard<std::mutex> lock(g_jit_mu);
-    JitEntry& e = g_jit_cache[source];
+    JitEntry& e = g_jit_cache[key];
     if (e.cubin.empty()) {
-        int32_t s = compile_cubin(source, &e.cubin);
-        if (s != TRS_OK) { g_jit_cache.erase(source); return s; }
+        int32_t s = compile_cubin(pw_generate_source(program, plan), &e.cubin);
+        if (s != TRS_OK) { g_jit_cache.erase(key); return s; }
     }
     if (load && !e.kernel) {
         cudaError_t err = cudaLibraryLoadData(&e.library, e.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
@@ -121,7 +122,7 @@ int32_t trs_pointwise_prepare(const trs_program* program, const trs_operand* inp
     if (klass) snprintf(klass, 16, "%s", plan.empty ? "empty" : (plan.tiled ? "tiled" : "vector"));
     if (plan.empty) return TRS_OK;
     JitEntry* entry = nullptr;
-    return get_kernel(pw_generate_source(program, plan), false, &entry);
+    return get_kernel(program, plan, false, &entry);
 }
 
 int32_t trs_pointwise(const trs_program* program, const trs_operand* inputs, const trs_operand* outputs,
@@ -133,7 +134,7 @@ int32_t trs_pointwise(const trs_program* program, const trs_operand* inputs, con
     DeviceGuard guard(stream->device);
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", stream->device);
     JitEntry* entry = nullptr;
-    TRS_TRY(get_kernel(pw_generate_source(program, plan), true, &entry));
+    TRS_TRY(get_kernel(program, plan, true, &entry));
     void* args[] = {&plan.params};
     // Programmatic dependent launch: the kernel starts with griddepcontrol.wait, so its blocks may be
     // scheduled while the stream's previous kernel drains (hides the launch gap between chained kernels).

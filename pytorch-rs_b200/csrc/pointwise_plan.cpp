@@ -574,6 +574,30 @@ extern "C" __global__ void __launch_bounds__(256) trs_pw(const Params p) {
 
 }  // namespace
 
+// Everything the generated source depends on, as a short byte string: the kernel cache is keyed by it so
+// that a cache hit does not have to build (and hash) kilobytes of source text per launch.
+std::string pw_cache_key(const trs_program* prog, const PwPlan& plan) {
+    std::string key;
+    key.reserve(64 + (size_t)prog->n_instrs * sizeof(trs_instr));
+    auto put = [&key](int v) { key.push_back((char)(v & 0xff)); key.push_back((char)((v >> 8) & 0xff)); };
+    put(plan.n_in); put(plan.n_out); put(plan.ndim); put(plan.unroll); put(plan.block); put(plan.tdim);
+    put((plan.has_tail ? 1 : 0) | (plan.wide_items ? 2 : 0) | (plan.wide_offsets ? 4 : 0) | (plan.tiled ? 8 : 0) | (plan.tile_vec ? 16 : 0));
+    for (int k = 0; k < plan.n_in; ++k) put(plan.in_kind[k]);
+    for (int o = 0; o < plan.n_out; ++o) put(plan.out_kind[o]);
+    put(prog->n_inputs); put(prog->n_instrs); put(prog->n_outputs);
+    for (int o = 0; o < prog->n_outputs; ++o) put(prog->outputs[o]);
+    for (int j = 0; j < prog->n_instrs; ++j) {
+        const trs_instr& in = prog->instrs[j];
+        put(in.op); put(in.a);
+        // only the fields the emitted text reads: `imm` of a constant, `b` of a binary op
+        const bool binary = in.op == TRS_OP_ADD || in.op == TRS_OP_SUB || in.op == TRS_OP_MUL || in.op == TRS_OP_DIV ||
+                            in.op == TRS_OP_RELU_VJP || in.op == TRS_OP_NE;
+        if (in.op == TRS_OP_CONST) key.append(reinterpret_cast<const char*>(&in.imm), sizeof in.imm);
+        else if (binary) put(in.b);
+    }
+    return key;
+}
+
 std::string pw_generate_source(const trs_program* prog, const PwPlan& plan) {
     std::ostringstream s;
     s << "#define NIN " << plan.n_in << "\n#define NOUT " << plan.n_out << "\n#define NDIM " << plan.ndim << "\n";

@@ -54,5 +54,6 @@ int32_t pw_make_plan(const trs_program* program, const trs_operand* inputs, cons
 // `trs_pw`.  Identical (program, class, kinds, ndim, flags) give identical text, which is the
 // cache key.
 std::string pw_generate_source(const trs_program* program, const PwPlan& plan);
+std::string pw_cache_key(const trs_program* program, const PwPlan& plan);
 
 }  // namespace trs
