@@ -370,3 +370,78 @@ def test_dlpack_export_is_zero_copy_and_keeps_the_layout():
     assert np.array_equal(shared.cpu().numpy(), (xs.T * 2.0).astype(np.float32))
     del out                     # the capsule keeps the storage alive
     assert np.array_equal(shared.cpu().numpy(), (xs.T * 2.0).astype(np.float32))
+
+
+# ---- transform VJPs: bits, accumulation over passes, freeing of value-dependent graphs ----------------------
+# Same scheme as the reference's tests/test_transpose_backward.py:9-146: gradients with awkward bit patterns
+# must arrive at the leaf untouched through t / transpose / permute of direct, offset and non-contiguous views.
+
+_GRADIENT_BITS = np.array([0x00000000, 0x80000000, 0x3F800001, 0xBF000001, 0x41234567, 0xC1234567,
+                           0x00800000, 0x80800000, 0x3EAAAAAB, 0xBEAAAAAB], dtype=np.uint32).view(np.float32)
+
+
+def _patterned(shape):
+    return np.resize(_GRADIENT_BITS, int(np.prod(shape))).reshape(shape).astype(np.float32)
+
+
+def _rank_two_source(kind, rows, cols):
+    """(leaf, rank-two view of it, function mapping a gradient of the view to the leaf's gradient)."""
+    if kind == "direct":
+        leaf = torch.zeros(rows, cols, device=DEV, requires_grad=True)
+        return leaf, leaf, lambda g: g
+    if kind == "offset":
+        leaf = torch.zeros(2, rows, cols, device=DEV, requires_grad=True)
+
+        def lift(g):
+            out = np.zeros((2, rows, cols), dtype=np.float32)
+            out[1] = g
+            return out
+        return leaf, leaf[1], lift
+    if kind == "noncontiguous":
+        leaf = torch.zeros(cols, rows, device=DEV, requires_grad=True)
+        return leaf, leaf.transpose(0, 1), lambda g: np.ascontiguousarray(g.T)
+    leaf = torch.zeros(cols, rows, 2, device=DEV, requires_grad=True)          # offset and non-contiguous
+
+    def lift(g):
+        out = np.zeros((cols, rows, 2), dtype=np.float32)
+        out[:, :, 1] = g.T
+        return out
+    return leaf, leaf.transpose(0, 2)[1], lift
+
+
+@pytest.mark.parametrize("kind,shape", [("direct", (1, 1)), ("direct", (1, 7)), ("direct", (7, 11)), ("offset", (5, 7)),
+                                        ("noncontiguous", (5, 7)), ("offset noncontiguous", (5, 7))])
+@pytest.mark.parametrize("op", ["t", "transpose", "permute"])
+def test_rank_two_transform_backward_bits_accumulation_and_freeing(kind, shape, op):
+    apply = {"t": lambda x: x.t(), "transpose": lambda x: torch.transpose(x, 0, 1), "permute": lambda x: x.permute(1, 0)}[op]
+    leaf, source, lift = _rank_two_source(kind, *shape)
+    transformed = apply(source)
+    weights = _patterned(tuple(transformed.shape))
+    loss = (transformed * torch.tensor(weights, device=DEV)).sum()
+    once = lift(np.ascontiguousarray(weights.T))
+    loss.backward()
+    assert np.array_equal(leaf.grad.numpy().view(np.uint32), once.view(np.uint32))
+    with pytest.raises(RuntimeError, match="backward through the graph a second time"):
+        loss.backward()                                             # the product saved its operands; they are freed
+    (apply(source) * torch.tensor(weights, device=DEV)).sum().backward()
+    twice = once + once
+    assert np.array_equal(leaf.grad.numpy().view(np.uint32), twice.view(np.uint32))
+    reusable = apply(source).sum()                                  # no saved values: the graph survives a pass
+    ones = lift(np.ones(tuple(source.shape), dtype=np.float32))
+    for _ in range(2):
+        reusable.backward()
+        twice = twice + ones
+        assert np.array_equal(leaf.grad.numpy().view(np.uint32), twice.view(np.uint32))
+
+
+def test_rank_three_permutation_backward_bits():
+    leaf = torch.zeros(2, 3, 5, device=DEV, requires_grad=True)
+    weights = _patterned((5, 2, 3))
+    loss = (leaf.permute(2, 0, 1) * torch.tensor(weights, device=DEV)).sum()
+    once = np.ascontiguousarray(weights.transpose(1, 2, 0))
+    loss.backward()
+    assert np.array_equal(leaf.grad.numpy().view(np.uint32), once.view(np.uint32))
+    with pytest.raises(RuntimeError, match="backward through the graph a second time"):
+        loss.backward()
+    (leaf.permute(2, 0, 1) * torch.tensor(weights, device=DEV)).sum().backward()
+    assert np.array_equal(leaf.grad.numpy().view(np.uint32), (once + once).view(np.uint32))
