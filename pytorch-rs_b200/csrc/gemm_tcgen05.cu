@@ -125,11 +125,28 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
-// kind::tf32, FP32 accumulate, A and B K-major, M=256 over the CTA pair (128 rows each), N=256.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+// kind::tf32, FP32 accumulate, M=256 over the CTA pair (128 rows each), N=256; bit 15 / 16 set = A / B is MN-major.
 constexpr uint32_t kInstrDescPair = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t accumulate) {
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p; }"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(kInstrDescPair), "r"(accumulate) : "memory");
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// MN-major operand tile (the only form kind::tf32 takes for it: 128-byte rows swizzled in 32-byte chunks):
+// 32 consecutive rows of the operand (128 bytes) per k, kRows k per group; groups of 32 rows lie kRows * 128
+// bytes apart (leading byte offset), atoms of 4 k 512 bytes apart (stride byte offset).
+template <int kRows>
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((kRows * 128) >> 4) << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;                            // SWIZZLE_128B_BASE32B
+    return d;
 }
 // Arrives on the barrier at this shared-memory offset in every CTA of `cta_mask` once the MMAs issued so far retire.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
@@ -155,6 +172,7 @@ struct EpilogueArgs {
     int tiles_m, tiles_n, total_tiles;
     int whole_tiles;      // work items [0, whole_tiles) are complete tiles; each later tile is two half-K items added atomically
     int total_items;
+    int a_mn, b_mn;       // pair kernel: the operand's tiles are MN-major (unit stride along its rows) instead of K-major
 };
 
 // Tile order: bands of 16 tile rows, walked column by column, so that the ~148 tiles in flight at
@@ -406,6 +424,7 @@ constexpr int PAIR_B_TILE_BYTES = (BN / 2) * PAIR_ROW_BYTES;
 constexpr int PAIR_STAGE_BYTES = 2 * PAIR_A_TILE_BYTES + 2 * PAIR_B_TILE_BYTES;  // 64 KiB per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_GROUP_M = 8;                                                   // bands of 8 x 256 rows
+constexpr bool kMnMajorOperands = true;                                           // read row-contiguous operands MN-major
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
@@ -457,10 +476,20 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                     const uint32_t full = map_to_cta(smem_u32(&full_bar[s]), 0);
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
-                    tma_load_3d_pair(base, &map_a_hi, full, kb * PAIR_BK, a_row, batch);
-                    tma_load_3d_pair(base + PAIR_A_TILE_BYTES, &map_a_lo, full, kb * PAIR_BK, a_row, batch);
-                    tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES, &map_b_hi, full, kb * PAIR_BK, b_row, batch);
-                    tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, kb * PAIR_BK, b_row, batch);
+                    if (e.a_mn) {
+                        tma_load_4d_pair(base, &map_a_hi, full, 0, kb * PAIR_BK, a_row >> 5, batch);
+                        tma_load_4d_pair(base + PAIR_A_TILE_BYTES, &map_a_lo, full, 0, kb * PAIR_BK, a_row >> 5, batch);
+                    } else {
+                        tma_load_3d_pair(base, &map_a_hi, full, kb * PAIR_BK, a_row, batch);
+                        tma_load_3d_pair(base + PAIR_A_TILE_BYTES, &map_a_lo, full, kb * PAIR_BK, a_row, batch);
+                    }
+                    if (e.b_mn) {
+                        tma_load_4d_pair(base + 2 * PAIR_A_TILE_BYTES, &map_b_hi, full, 0, kb * PAIR_BK, b_row >> 5, batch);
+                        tma_load_4d_pair(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, 0, kb * PAIR_BK, b_row >> 5, batch);
+                    } else {
+                        tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES, &map_b_hi, full, kb * PAIR_BK, b_row, batch);
+                        tma_load_3d_pair(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES, &map_b_lo, full, kb * PAIR_BK, b_row, batch);
+                    }
                 }
             }
             // stay until the leader's last commits have arrived on this CTA's barriers
@@ -474,6 +503,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             // ---- MMA issuer (leader CTA only) ----
             bool failed = false;
             uint32_t g = 0, it = 0;
+            const uint32_t idesc = kInstrDescPair | (e.a_mn ? (1u << 15) : 0u) | (e.b_mn ? (1u << 16) : 0u);
             for (int w = pair; w < e.total_items && !failed; w += pairs, ++it) {
                 int t, kb_begin, kb_end;
                 bool split;
@@ -487,14 +517,19 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                     if (!mbar_wait(smem_u32(&full_bar[s]), (g / PAIR_STAGES) & 1)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
-                    const uint64_t a_hi = smem_desc<PAIR_ROW_BYTES>(base), a_lo = smem_desc<PAIR_ROW_BYTES>(base + PAIR_A_TILE_BYTES);
-                    const uint64_t b_hi = smem_desc<PAIR_ROW_BYTES>(base + 2 * PAIR_A_TILE_BYTES), b_lo = smem_desc<PAIR_ROW_BYTES>(base + 2 * PAIR_A_TILE_BYTES + PAIR_B_TILE_BYTES);
+                    const uint32_t a0 = base, a1 = base + PAIR_A_TILE_BYTES, b0 = base + 2 * PAIR_A_TILE_BYTES, b1 = b0 + PAIR_B_TILE_BYTES;
+                    const uint64_t a_hi = e.a_mn ? smem_desc_mn<PAIR_BK>(a0) : smem_desc<PAIR_ROW_BYTES>(a0);
+                    const uint64_t a_lo = e.a_mn ? smem_desc_mn<PAIR_BK>(a1) : smem_desc<PAIR_ROW_BYTES>(a1);
+                    const uint64_t b_hi = e.b_mn ? smem_desc_mn<PAIR_BK>(b0) : smem_desc<PAIR_ROW_BYTES>(b0);
+                    const uint64_t b_lo = e.b_mn ? smem_desc_mn<PAIR_BK>(b1) : smem_desc<PAIR_ROW_BYTES>(b1);
+                    // 8 k per MMA: 32 bytes along a K-major row, or one 8-k-row atom (1024 bytes) of an MN-major tile
+                    const uint64_t a_step = e.a_mn ? (1024 >> 4) : (32 >> 4), b_step = e.b_mn ? (1024 >> 4) : (32 >> 4);
 #pragma unroll
                     for (int k = 0; k < PAIR_BK / 8; ++k) {
-                        const uint64_t step = (uint64_t)((k * 8 * 4) >> 4);
-                        umma_tf32_pair(d, a_lo + step, b_hi + step, (kb != kb_begin) || (k != 0));
-                        umma_tf32_pair(d, a_hi + step, b_lo + step, 1u);
-                        umma_tf32_pair(d, a_hi + step, b_hi + step, 1u);
+                        const uint64_t sa = a_step * k, sb = b_step * k;
+                        umma_tf32_pair(d, a_lo + sa, b_hi + sb, idesc, (kb != kb_begin) || (k != 0));
+                        umma_tf32_pair(d, a_hi + sa, b_lo + sb, idesc, 1u);
+                        umma_tf32_pair(d, a_hi + sa, b_hi + sb, idesc, 1u);
                     }
                     umma_commit_pair(smem_u32(&empty_bar[s]), 3);
                 }
@@ -696,6 +731,32 @@ int32_t make_operand_map(CUtensorMap* map, const float* base, long long rows, lo
     return TRS_OK;
 }
 
+// Map over an operand whose rows are unit-stride in memory ([k, rows] with `pitch` elements between k):
+// dims {32 rows, k, rows / 32, batch}, so that one box lands as groups of 32 rows x bk k x 128 bytes, swizzled in
+// 32-byte chunks -- the MN-major tile form of smem_desc_mn.  `rows` must be a multiple of 32.
+int32_t make_mn_operand_map(CUtensorMap* map, const float* base, long long rows, long long k_extent, long long batch,
+                            long long pitch, long long batch_stride, int box_rows, int bk) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[4] = {32, (cuuint64_t)k_extent, (cuuint64_t)(rows / 32), (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)pitch * 4, 128, (cuuint64_t)batch_stride * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)bk, (cuuint32_t)(box_rows / 32), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TRS_ERR_CUDA, "cuTensorMapEncodeTiled (MN-major) failed with code %d", (int)r);
+    return TRS_OK;
+}
+
+// Whether the pair kernel can read the operand MN-major as it lies: unit stride along its rows, rows a multiple
+// of 32 (a box never straddles the end of a k line), 16-byte aligned lines.
+bool mn_major_ok(const float* src, long long batch, long long rows, long long batch_stride, long long row_stride, long long k_stride, long long k) {
+    if (row_stride != 1 || rows % 32 != 0 || (reinterpret_cast<uintptr_t>(src) & 15u) != 0 || k_stride % 4 != 0 || k_stride < rows) return false;
+    if (batch > 1 && (batch_stride % 4 != 0 || batch_stride < k * k_stride)) return false;
+    return k >= 1;
+}
+
 struct DeviceWords {
     unsigned int* error = nullptr;
     unsigned int* nonfinite = nullptr;
@@ -818,18 +879,35 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     bool b_raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
     if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM, bk) != TRS_OK) a_raw = false;
     if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box, bk) != TRS_OK) b_raw = false;
-    TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
-    TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
-    if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
-    TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
-    if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
-    TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
+    // An operand that is unit-stride along its rows (a transposed view, or the right operand of a plain A @ B) is
+    // read MN-major as it lies by the pair kernel; only its lo plane, in the same [k, rows] order, is prepared.
+    bool a_mn = pair && kMnMajorOperands && !a_raw && mn_major_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
+    bool b_mn = pair && kMnMajorOperands && !b_raw && mn_major_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
+    if (a_mn && make_mn_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_col_stride, g.batch > 1 ? g.a_batch_stride : g.k * g.a_col_stride, BM, bk) != TRS_OK) a_mn = false;
+    if (b_mn && make_mn_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_row_stride, g.batch > 1 ? g.b_batch_stride : g.k * g.b_row_stride, b_box, bk) != TRS_OK) b_mn = false;
+    if (a_mn) {
+        // lo plane [batch, k, m]: the k-fast kernel with the roles of the axes exchanged (its "rows" are k, its "k" is m)
+        TRS_TRY(launch_split(g.a, g.batch, g.k, g.m, g.m, g.a_batch_stride, g.a_col_stride, 1, a_hi, a_lo, words->nonfinite, stream, 1));
+        TRS_TRY(make_mn_operand_map(&ma_lo, a_lo, g.m, g.k, g.batch, g.m, g.k * g.m, BM, bk));
+    } else {
+        TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
+        if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
+        TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
+    }
+    if (b_mn) {
+        TRS_TRY(launch_split(g.b, g.batch, g.k, g.n, g.n, g.b_batch_stride, g.b_row_stride, 1, b_hi, b_lo, words->nonfinite, stream, 1));
+        TRS_TRY(make_mn_operand_map(&mb_lo, b_lo, g.n, g.k, g.batch, g.n, g.k * g.n, b_box, bk));
+    } else {
+        TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
+        if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
+        TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
+    }
     const long long tile_rows = pair ? 2 * BM : BM;
     const long long tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + BN - 1) / BN;
     const long long total_tiles = tiles_m * tiles_n * g.batch;
     if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
     EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / bk), g.epilogue,
-                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles};
+                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles, a_mn ? 1 : 0, b_mn ? 1 : 0};
     // units that work side by side: SMs, or resident CTA pairs
     const long long units = pair ? words->pair_clusters : sm_count(stream->device);
     // A last round that occupies at most half of the units is cut in two along K (plain products on
