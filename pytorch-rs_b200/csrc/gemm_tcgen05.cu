@@ -7,12 +7,12 @@
 // lo*lo term (relative 2^-22), so the result stays within the path's rel 1e-5*sqrt(K) tolerance.
 //
 // Kernels:
-//   split_tf32_*            prepare the operand planes K-major ([rows, K_pad], K_pad a multiple of 32,
-//                           zero padded) in scratch memory.  A K-major, 16-byte aligned operand is fed
-//                           to the MMA as it lies (the MMA drops the low 13 mantissa bits, i.e. it sees
-//                           hi = truncation) and only its lo plane is written; transposed views (.mT
-//                           operands, the backward GEMMs) are re-laid into hi and lo planes here, so the
-//                           GEMM itself sees one layout only.
+//   split_tf32_*            prepare operand planes in scratch memory.  An aligned operand is fed to the
+//                           MMA as it lies (the MMA drops the low 13 mantissa bits, i.e. it sees
+//                           hi = truncation) and only its lo plane is written, in the operand's own
+//                           order: K-major ([rows, K_pad], K_pad a multiple of 32, zero padded) or, for
+//                           row-contiguous operands on the pair kernel, MN-major ([K, rows]).  Other
+//                           operands are re-laid into K-major hi and lo planes through shared memory.
 //   gemm_tf32x3_kernel      persistent, one CTA per 128x256 output tile.  Warp 0 drives TMA (no
 //                           multicast) into a 4-stage ring of {A_hi, A_lo, B_hi, B_lo} 64-byte-swizzled
 //                           tiles, warp 1 issues 6 tcgen05.mma per stage into one of two 128x256 FP32
@@ -20,7 +20,8 @@
 //                           apply the epilogue.
 //   gemm_tf32x3_pair_kernel the same pipeline on a cluster of two CTAs per 256x256 tile
 //                           (tcgen05.mma.cta_group::2): each CTA stages half of B, which takes the
-//                           shared-memory port off the critical path.  The default where M allows.
+//                           shared-memory port off the critical path; reads K-major and MN-major
+//                           operand tiles.  The default where M allows.
 // Every wait on an mbarrier is bounded; on a timeout the kernel records an error word, releases
 // its tensor memory and returns, and the host reports TRS_ERR_DEVICE_STATUS.
 #include <cuda.h>
@@ -424,7 +425,8 @@ constexpr int PAIR_B_TILE_BYTES = (BN / 2) * PAIR_ROW_BYTES;
 constexpr int PAIR_STAGE_BYTES = 2 * PAIR_A_TILE_BYTES + 2 * PAIR_B_TILE_BYTES;  // 64 KiB per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_GROUP_M = 8;                                                   // bands of 8 x 256 rows
-constexpr bool kMnMajorOperands = true;                                           // read row-contiguous operands MN-major
+constexpr bool kMnMajorOperands = true;                                           // read row-contiguous operands MN-major ...
+constexpr long long kMnMajorMaxReuse = 4096;                                      // ... when each element is used at most this often
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
@@ -881,8 +883,12 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box, bk) != TRS_OK) b_raw = false;
     // An operand that is unit-stride along its rows (a transposed view, or the right operand of a plain A @ B) is
     // read MN-major as it lies by the pair kernel; only its lo plane, in the same [k, rows] order, is prepared.
-    bool a_mn = pair && kMnMajorOperands && !a_raw && mn_major_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
-    bool b_mn = pair && kMnMajorOperands && !b_raw && mn_major_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
+    // Measured: the MMA reads an MN-major tile 1-3 % slower than a K-major one, while re-laying an operand costs
+    // 4 more bytes of HBM traffic per element; the operand's reuse (the other output extent) decides which is cheaper.
+    bool a_mn = pair && kMnMajorOperands && !a_raw && g.n <= kMnMajorMaxReuse &&
+                mn_major_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
+    bool b_mn = pair && kMnMajorOperands && !b_raw && g.m <= kMnMajorMaxReuse &&
+                mn_major_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
     if (a_mn && make_mn_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_col_stride, g.batch > 1 ? g.a_batch_stride : g.k * g.a_col_stride, BM, bk) != TRS_OK) a_mn = false;
     if (b_mn && make_mn_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_row_stride, g.batch > 1 ? g.b_batch_stride : g.k * g.b_row_stride, b_box, bk) != TRS_OK) b_mn = false;
     if (a_mn) {
