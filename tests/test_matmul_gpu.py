@@ -202,3 +202,29 @@ def test_pair_kernel_with_two_k_major_operands(m, n, k):
     c1, _ = run(a, wt.mT, "tcgen05_3xtf32")
     if (m, n, k) != (2560, 2304, 288):
         assert np.array_equal(c.view(np.uint32), c1.view(np.uint32))
+
+
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_batched_products_with_row_contiguous_operands(algo):
+    # bmm whose operands are unit-stride along their rows: X.mT [b, m, k] over X [b, k, m], and W [b, k, n] row-major.
+    # The pair kernel reads both MN-major through a 4-D tensor map with the batch as its outer dimension.
+    batch, m, n, k = 3, 256, 320, 96
+    xt = RefTensor.from_numpy(rnd(70, batch, k, m))
+    w = RefTensor.from_numpy(rnd(71, batch, k, n, scale=1 / np.sqrt(k)))
+    c, _ = run(xt.mT, w, algo)
+    assert c.shape == (batch, m, n)
+    for i in range(batch):
+        want64 = xt.logical()[i].astype(np.float64).T @ w.logical()[i].astype(np.float64)
+        assert np.abs(c[i] - want64).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(want64 ** 2))
+        ok, worst = matmul_tolerance_ok(c[i], xt.select0(i).mT.matmul(w.select0(i)).logical(), k)
+        assert ok, worst
+
+
+def test_split_k_tail_with_row_contiguous_operands():
+    # 90 tile pairs on 74 SM pairs with 16 K blocks: the last 16 pairs are cut in two along K and added atomically,
+    # with both operands read MN-major.
+    m, n, k = 2560, 2304, 512
+    at, b = RefTensor.from_numpy(rnd(72, k, m)).mT, RefTensor.from_numpy(rnd(73, k, n, scale=1 / np.sqrt(k)))
+    c, _ = run(at, b, "tcgen05_3xtf32_2cta")
+    ref64 = at.logical().astype(np.float64) @ b.logical().astype(np.float64)
+    assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(ref64 ** 2))
