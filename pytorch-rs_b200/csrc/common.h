@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <utility>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -67,6 +68,32 @@ struct DeviceGuard {
 };
 
 inline void count_launch(int64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+#ifdef __CUDACC__
+// Launch with programmatic stream serialization: the kernel's blocks may become resident while the
+// stream's previous kernel drains.  Only for kernels that execute pdl_wait() before their first access
+// to memory another kernel may have written.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+// Waits until the kernels this one depends on have completed and their writes are visible, then lets the
+// next kernel of the stream start taking the slots this grid frees.  A no-op in an ordinary launch.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+#endif
 
 int32_t check_stream(trs_stream s);
 int sm_count(int device);

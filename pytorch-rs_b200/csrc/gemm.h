@@ -3,8 +3,8 @@
 #include "common.h"
 
 namespace trs {
-// `gate`: optional device word; when non-NULL the kernel returns at once unless *gate != 0.
-int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate = nullptr);
+// `gate`: optional device word; when non-NULL the kernel returns at once unless *gate == epoch.
+int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate = nullptr, unsigned int epoch = 0);
 // Whether the tensor-core path can take this descriptor (alignment and size rules).
 bool gemm_tc_eligible(const trs_gemm_desc& g);
 // Whether the two-CTA (256x256 tiles) variant suits this descriptor better than the one-CTA kernel.

@@ -49,8 +49,9 @@ constexpr int K_PAD = 32;                             // operand planes are padd
 
 // Error word written by a kernel whose bounded wait ran out (0 = fine).
 __device__ unsigned int g_gemm_error;
-// Set by the split kernel when an operand holds inf/NaN (the split cannot represent those).
-__device__ unsigned int g_nonfinite_seen;
+// Written by the split kernels when an operand holds inf/NaN (the split cannot represent those): each
+// tensor-core matmul call owns word (epoch % 8) and marks it with its epoch, so nothing has to be cleared.
+__device__ unsigned int g_nonfinite_seen[8];
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -309,6 +310,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                           // barriers and tensor memory are set up while the previous kernel drains
 
     if (warp == 0) {
         if (lane == 0) {
@@ -459,6 +461,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
     cluster_sync_all();                                   // the peer's barriers are initialised before anything signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                           // barriers and tensor memory are set up while the previous kernel drains
 
     if (warp == 0) {
         if (lane == 0) {
@@ -587,12 +590,13 @@ struct SplitArgs {
     long long rows, k, k_pad;
     unsigned int* nonfinite;
     int lo_only;          // the source itself serves as the hi operand (the MMA drops the low 13 bits): hi = truncation
+    unsigned int epoch;   // value stored to *nonfinite when an inf / NaN is met
 };
 
-__device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsigned int* nonfinite, bool truncate_hi = false) {
+__device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsigned int* nonfinite, unsigned int epoch, bool truncate_hi = false) {
     const uint32_t bits = __float_as_uint(a);
     if ((bits & 0x7f800000u) == 0x7f800000u) {         // inf / NaN: not representable by the split
-        atomicOr(nonfinite, 1u);
+        *reinterpret_cast<volatile unsigned int*>(nonfinite) = epoch;
         hi = a; lo = 0.0f;
         return;
     }
@@ -612,6 +616,7 @@ __device__ __forceinline__ void split_value(float a, float& hi, float& lo, unsig
 
 // Source unit-stride along k: each thread converts 4 consecutive k of one row.
 __global__ void __launch_bounds__(256) split_tf32_kfast_kernel(const SplitArgs a, int vec) {
+    pdl_wait();
     const long long quads = a.k_pad >> 2;
     const long long total = a.rows * quads;
     const long long batch = blockIdx.y;
@@ -631,7 +636,7 @@ __global__ void __launch_bounds__(256) split_tf32_kfast_kernel(const SplitArgs a
         }
         float h[4], l[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) split_value(v[e], h[e], l[e], a.nonfinite, a.lo_only != 0);
+        for (int e = 0; e < 4; ++e) split_value(v[e], h[e], l[e], a.nonfinite, a.epoch, a.lo_only != 0);
         if (!a.lo_only) *reinterpret_cast<float4*>(hi + r * a.k_pad + k0) = make_float4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<float4*>(lo + r * a.k_pad + k0) = make_float4(l[0], l[1], l[2], l[3]);
     }
@@ -640,6 +645,7 @@ __global__ void __launch_bounds__(256) split_tf32_kfast_kernel(const SplitArgs a
 // Any other source layout (unit stride along rows, or fully strided): 32x32 tiles through shared
 // memory, read along the rows axis, written along k.
 __global__ void __launch_bounds__(256) split_tf32_tiled_kernel(const SplitArgs a) {
+    pdl_wait();
     __shared__ float tile[32][33];
     const long long batch = blockIdx.z;
     const float* src = a.src + batch * a.batch_stride;
@@ -658,7 +664,7 @@ __global__ void __launch_bounds__(256) split_tf32_tiled_kernel(const SplitArgs a
         const long long r = r0 + ty + 8 * j, k = k0 + tx;
         if (r < a.rows && k < a.k_pad) {
             float h, l;
-            split_value(tile[tx][ty + 8 * j], h, l, a.nonfinite);
+            split_value(tile[tx][ty + 8 * j], h, l, a.nonfinite, a.epoch);
             hi[r * a.k_pad + k] = h;
             lo[r * a.k_pad + k] = l;
         }
@@ -668,6 +674,7 @@ __global__ void __launch_bounds__(256) split_tf32_tiled_kernel(const SplitArgs a
 // Source unit-stride along rows (a transposed view) and 16-byte aligned: 64x64 tiles, float4 reads
 // along rows, float4 hi/lo writes along k.
 __global__ void __launch_bounds__(256) split_tf32_tiled64_kernel(const SplitArgs a) {
+    pdl_wait();
     __shared__ float tile[64][65];                       // [k][row]
     const long long batch = blockIdx.z;
     const float* src = a.src + batch * a.batch_stride;
@@ -691,7 +698,7 @@ __global__ void __launch_bounds__(256) split_tf32_tiled64_kernel(const SplitArgs
         if (r < a.rows && k < a.k_pad) {
             float h[4], l[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) split_value(tile[q4 + e][rl], h[e], l[e], a.nonfinite);
+            for (int e = 0; e < 4; ++e) split_value(tile[q4 + e][rl], h[e], l[e], a.nonfinite, a.epoch);
             *reinterpret_cast<float4*>(hi + r * a.k_pad + k) = make_float4(h[0], h[1], h[2], h[3]);
             *reinterpret_cast<float4*>(lo + r * a.k_pad + k) = make_float4(l[0], l[1], l[2], l[3]);
         }
@@ -764,14 +771,17 @@ struct DeviceWords {
     unsigned int* nonfinite = nullptr;
     bool launched = false;
     bool smem_set = false;
+    unsigned int epoch = 0;     // tag of the latest tensor-core matmul call on this device
     int pair_clusters = 0;      // CTA pairs of the two-CTA kernel that can be resident at once
 };
 DeviceWords g_words[16];
 std::mutex g_words_mu;
 
-int32_t device_words(int device, DeviceWords** out) {
+int32_t device_words(int device, DeviceWords** out, unsigned int* epoch) {
     std::lock_guard<std::mutex> lock(g_words_mu);
     DeviceWords& w = g_words[device];
+    if (++w.epoch == 0) ++w.epoch;                       // 0 is the words' initial value: never a tag
+    *epoch = w.epoch;
     if (!w.error) {
         TRS_CUDA(cudaGetSymbolAddress((void**)&w.error, g_gemm_error));
         TRS_CUDA(cudaGetSymbolAddress((void**)&w.nonfinite, g_nonfinite_seen));
@@ -814,22 +824,22 @@ bool raw_hi_ok(const float* src, long long batch, long long rows, long long batc
 }
 
 int32_t launch_split(const float* src, long long batch, long long rows, long long k, long long k_pad, long long batch_stride,
-                     long long row_stride, long long k_stride, float* hi, float* lo, unsigned int* nonfinite, trs_stream stream,
-                     int lo_only = 0) {
-    SplitArgs a{src, hi, lo, batch_stride, row_stride, k_stride, rows, k, k_pad, nonfinite, lo_only};
+                     long long row_stride, long long k_stride, float* hi, float* lo, unsigned int* nonfinite, unsigned int epoch,
+                     trs_stream stream, int lo_only = 0) {
+    SplitArgs a{src, hi, lo, batch_stride, row_stride, k_stride, rows, k, k_pad, nonfinite, lo_only, epoch};
     if (k_stride == 1 || k == 1) {
         const int vec = (row_stride % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
         const long long total = rows * (k_pad >> 2);
         unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)sm_count(stream->device) * 32);
-        split_tf32_kfast_kernel<<<dim3(std::max(grid, 1u), (unsigned)batch), 256, 0, stream->stream>>>(a, vec);
+        TRS_CUDA(launch_dependent(split_tf32_kfast_kernel, dim3(std::max(grid, 1u), (unsigned)batch), dim3(256), 0, stream->stream, a, vec));
     } else if (row_stride == 1 && rows % 4 == 0 && k_stride % 4 == 0 && batch_stride % 4 == 0 &&
                (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
         dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((k_pad + 63) / 64), (unsigned)batch);
         if (grid.y > 65535) return fail(TRS_ERR_UNSUPPORTED, "inner dimension too large for the operand split");
-        split_tf32_tiled64_kernel<<<grid, 256, 0, stream->stream>>>(a);
+        TRS_CUDA(launch_dependent(split_tf32_tiled64_kernel, grid, dim3(256), 0, stream->stream, a));
     } else {
         dim3 grid((unsigned)((rows + 31) / 32), (unsigned)(k_pad / 32), (unsigned)batch);   // k_pad is a multiple of 32
-        split_tf32_tiled_kernel<<<grid, 256, 0, stream->stream>>>(a);
+        TRS_CUDA(launch_dependent(split_tf32_tiled_kernel, grid, dim3(256), 0, stream->stream, a));
     }
     TRS_CUDA(cudaGetLastError());
     count_launch();
@@ -864,14 +874,15 @@ size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g) {
 // Runs split + GEMM with caller-provided scratch of gemm_tc_scratch_bytes(g).
 int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream stream) {
     DeviceWords* words = nullptr;
-    TRS_TRY(device_words(stream->device, &words));
+    unsigned int epoch = 0;
+    TRS_TRY(device_words(stream->device, &words, &epoch));
+    unsigned int* nonfinite = words->nonfinite + (epoch & 7u);
     const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
     const long long a_plane = g.batch * g.m * k_pad, b_plane = g.batch * g.n * k_pad;
     float* a_hi = scratch;
     float* a_lo = a_hi + a_plane;
     float* b_hi = a_lo + a_plane;
     float* b_lo = b_hi + b_plane;
-    TRS_CUDA(cudaMemsetAsync(words->nonfinite, 0, sizeof(unsigned int), stream->stream));
     // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const bool pair = g.algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
@@ -893,18 +904,18 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
     if (b_mn && make_mn_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_row_stride, g.batch > 1 ? g.b_batch_stride : g.k * g.b_row_stride, b_box, bk) != TRS_OK) b_mn = false;
     if (a_mn) {
         // lo plane [batch, k, m]: the k-fast kernel with the roles of the axes exchanged (its "rows" are k, its "k" is m)
-        TRS_TRY(launch_split(g.a, g.batch, g.k, g.m, g.m, g.a_batch_stride, g.a_col_stride, 1, a_hi, a_lo, words->nonfinite, stream, 1));
+        TRS_TRY(launch_split(g.a, g.batch, g.k, g.m, g.m, g.a_batch_stride, g.a_col_stride, 1, a_hi, a_lo, nonfinite, epoch, stream, 1));
         TRS_TRY(make_mn_operand_map(&ma_lo, a_lo, g.m, g.k, g.batch, g.m, g.k * g.m, BM, bk));
     } else {
-        TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, words->nonfinite, stream, a_raw));
+        TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, nonfinite, epoch, stream, a_raw));
         if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
         TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
     }
     if (b_mn) {
-        TRS_TRY(launch_split(g.b, g.batch, g.k, g.n, g.n, g.b_batch_stride, g.b_row_stride, 1, b_hi, b_lo, words->nonfinite, stream, 1));
+        TRS_TRY(launch_split(g.b, g.batch, g.k, g.n, g.n, g.b_batch_stride, g.b_row_stride, 1, b_hi, b_lo, nonfinite, epoch, stream, 1));
         TRS_TRY(make_mn_operand_map(&mb_lo, b_lo, g.n, g.k, g.batch, g.n, g.k * g.n, b_box, bk));
     } else {
-        TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, words->nonfinite, stream, b_raw));
+        TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, nonfinite, epoch, stream, b_raw));
         if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
         TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
     }
@@ -926,14 +937,22 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
         TRS_CUDA(cudaMemsetAsync(g.c, 0, (size_t)(g.batch * g.m * g.n) * sizeof(float), stream->stream));
     }
     const unsigned grid = (unsigned)std::min<long long>(e.total_items, units);
-    if (pair) gemm_tf32x3_pair_kernel<<<2 * grid, 192, PAIR_SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
-    else gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
-    TRS_CUDA(cudaGetLastError());
+    const bool zeroed_c = e.total_items != e.total_tiles;       // a memset of C sits between the preparation and this kernel
+    if (zeroed_c) {
+        // ordinary launch: programmatic serialization is between kernels only
+        if (pair) gemm_tf32x3_pair_kernel<<<2 * grid, 192, PAIR_SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
+        else gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
+        TRS_CUDA(cudaGetLastError());
+    } else if (pair) {
+        TRS_CUDA(launch_dependent(gemm_tf32x3_pair_kernel, dim3(2 * grid), dim3(192), PAIR_SMEM_BYTES, stream->stream, ma_hi, ma_lo, mb_hi, mb_lo, e));
+    } else {
+        TRS_CUDA(launch_dependent(gemm_tf32x3_kernel, dim3(grid), dim3(192), SMEM_BYTES, stream->stream, ma_hi, ma_lo, mb_hi, mb_lo, e));
+    }
     count_launch();
     words->launched = true;
     // inf / NaN operands: recompute with the exact-FP32 kernel (a no-op launch when none were seen),
     // which keeps the reference's inf/NaN classification of the result.
-    TRS_TRY(gemm_simt_launch(g, stream, words->nonfinite));
+    TRS_TRY(gemm_simt_launch(g, stream, nonfinite, epoch));
     return TRS_OK;
 }
 
