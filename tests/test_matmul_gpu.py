@@ -228,3 +228,28 @@ def test_split_k_tail_with_row_contiguous_operands():
     c, _ = run(at, b, "tcgen05_3xtf32_2cta")
     ref64 = at.logical().astype(np.float64) @ b.logical().astype(np.float64)
     assert np.abs(c - ref64).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(ref64 ** 2))
+
+
+def test_batched_product_over_several_rounds_of_tiles():
+    # 32 batches of 1024 x 1024 outputs are 7 rounds of tile pairs on the persistent pair kernel; every batch must
+    # come out as if done alone, with the fused bias + relu epilogue and its pre-activation output.
+    batch, m, n, k = 32, 1024, 1024, 64
+    x = rnd(80, batch, m, k)
+    w = rnd(81, batch, n, k, scale=1 / np.sqrt(k))
+    bias = np.random.default_rng(82).uniform(-0.1, 0.1, n).astype(np.float32)
+    c, pre = run(RefTensor.from_numpy(x), RefTensor.from_numpy(w).mT, "tcgen05_3xtf32_2cta", bias=bias, epilogue="bias_relu",
+                 want_preact=True)
+    for i in range(batch):
+        want64 = x[i].astype(np.float64) @ w[i].astype(np.float64).T + bias
+        assert np.abs(pre[i] - want64).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(want64 ** 2)) + 1e-6, i
+    assert np.array_equal(c.view(np.uint32), RefTensor.from_numpy(pre).relu().logical().view(np.uint32))
+    # the same product in one piece by the one-CTA kernel: identical bits (same products, same k order)
+    c1, pre1 = run(RefTensor.from_numpy(x), RefTensor.from_numpy(w).mT, "tcgen05_3xtf32", bias=bias, epilogue="bias_relu",
+                   want_preact=True)
+    assert np.array_equal(pre.view(np.uint32), pre1.view(np.uint32))
+    # row-major right operand (MN-major tiles), batched
+    wt = np.ascontiguousarray(np.swapaxes(w, 1, 2))
+    c2, _ = run(RefTensor.from_numpy(x), RefTensor.from_numpy(wt), "tcgen05_3xtf32_2cta")
+    for i in (0, 8, 9, 31):
+        want64 = x[i].astype(np.float64) @ wt[i].astype(np.float64)
+        assert np.abs(c2[i] - want64).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(want64 ** 2)), i
