@@ -6,6 +6,7 @@
 // with separate multiply and add roundings; this kernel accumulates k ascending per thread with
 // fused multiply-add, which differs by rounding only (tolerance rel 1e-5*sqrt(K) in the tests).
 #include <algorithm>
+#include <mutex>
 
 #include "common.h"
 #include "gemm.h"
@@ -140,6 +141,17 @@ int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsign
     const bool b_nfast = g.b_col_stride == 1 || g.b_row_stride != 1;
     auto kernel = a_kfast ? (b_nfast ? gemm_simt_kernel<true, true> : gemm_simt_kernel<true, false>)
                           : (b_nfast ? gemm_simt_kernel<false, true> : gemm_simt_kernel<false, false>);
+    if (gate) {
+        // A gated launch sits between tensor-core GEMMs and their preparation kernels: keep their shared-memory
+        // configuration, so that no SM has to drain to switch it for a kernel that returns at once.
+        static std::once_flag once;
+        std::call_once(once, [] {
+            cudaFuncSetAttribute(gemm_simt_kernel<true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(gemm_simt_kernel<true, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(gemm_simt_kernel<false, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(gemm_simt_kernel<false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        });
+    }
     TRS_CUDA(launch_dependent(kernel, dim3(grid), dim3(256), 0, stream->stream, g, gate, epoch, tiles_x, tiles_y, total));
     count_launch();
     return TRS_OK;
