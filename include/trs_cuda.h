@@ -21,6 +21,9 @@
  *   - work is enqueued on the given trs_stream and returns immediately; only
  *     trs_stream_sync, trs_device_sync and trs_memcpy_d2h (pageable) block.
  *   - thread-safe per device; callable with the host interpreter lock held.
+ *   - scratch memory the library needs inside a call is taken from and returned to the device cache in the
+ *     order of the call's stream (see trs_malloc_async), so calls on different streams of one device never
+ *     share scratch that is still in use.
  *   - there is no CPU fallback: without a CUDA device every compute entry
  *     point returns TRS_ERR_NO_DEVICE.
  */
@@ -52,6 +55,7 @@ typedef enum trs_status {
 
 typedef struct trs_stream_s* trs_stream;   /* a CUDA stream bound to one device */
 typedef struct trs_event_s* trs_event;
+typedef struct trs_comm_s* trs_comm;       /* one rank's end of a multi-process communicator */
 
 /* A strided view of a float32 device buffer (reference: storage + shape + strides + offset,
  * src/tensor.rs:212-221).  Element (i0..i{rank-1}) lives at base[offset + sum(i_k * stride[k])]. */
@@ -138,6 +142,13 @@ int32_t trs_device_count(int32_t* count);
 int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length);
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr);       /* cached blocks; Storage::from_owned */
 int32_t trs_free(int32_t device, void* ptr);                        /* Storage drop */
+/* Stream-ordered forms.  trs_free_async hands the block back while work that uses it may still be queued on
+ * `stream`; the cache remembers that stream.  trs_malloc_async may return such a block at once to the same
+ * stream (stream order protects it); for any other stream it first makes that stream wait for the work the
+ * freeing stream had queued.  Plain trs_malloc only returns a remembered block once its stream has drained,
+ * and plain trs_free states that nothing queued anywhere still uses the block. */
+int32_t trs_malloc_async(int32_t device, size_t bytes, trs_stream stream, void** ptr);
+int32_t trs_free_async(int32_t device, void* ptr, trs_stream stream);
 int32_t trs_empty_cache(int32_t device);
 int32_t trs_memory_stats(int32_t device, int64_t* bytes_in_use, int64_t* bytes_reserved);
 int32_t trs_malloc_host(size_t bytes, void** ptr);                  /* pinned staging memory */
@@ -198,6 +209,9 @@ int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, 
  * array: two calls whose kernels can overlap on the GPU (different streams) race and must be ordered
  * by the caller.  Nothing has to be cleared between calls. */
 int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, float* out, trs_stream stream);
+/* The row chunking trs_colsum_f32_noalloc uses on a GPU with `sm_count` SMs (no launch, no device needed):
+ * chunks * cols never exceeds the fixed array.  No counterpart in the reference. */
+int32_t trs_colsum_noalloc_geometry(int32_t sm_count, int64_t rows, int64_t cols, int32_t* chunks, int64_t* rows_per_chunk);
 
 /* ---- matmul ----------------------------------------------------------------------------------
  * Honours float32 matmul precision "highest" (python/torch_rs/__init__.py:81-85): either exact
@@ -206,7 +220,63 @@ int32_t trs_matmul_f32(const trs_gemm_desc* desc, trs_stream stream);
 /* Which algorithm TRS_GEMM_AUTO resolves to for this descriptor (no launch). */
 int32_t trs_matmul_select_algo(const trs_gemm_desc* desc, int32_t* algo);
 
+/* Prepared operand planes for the tensor-core matmul.  New: the reference multiplies FP32 values
+ * directly (src/tensor.rs:3919-3966) and needs no operand preparation.  The 3xTF32 split feeds the
+ * tensor core each operand element a as hi = a with its low 13 mantissa bits dropped (read in place)
+ * and lo = tf32(a - hi), which otherwise costs a pass over the operand in every call.  A reference
+ * Storage is immutable after construction (src/storage.rs:7-18), so the lo values are a pure function
+ * of a storage: a host may compute them once (trs_split_lo_f32), keep them beside the storage, and hand
+ * them to every matmul that reads it; a matmul can also write the lo values of its own result while it
+ * stores it, for the matmul that consumes the result next.
+ *   a_lo / b_lo  lo image of A / B: the lo value of the element at a[i] is at a_lo[i], for every i the
+ *                descriptor's strides reach (the same base offset and strides as the operand); NULL =
+ *                prepare per call.  Ignored where the kernel has to re-lay the operand anyway
+ *                (trs_matmul_plan tells).
+ *   a_flag/b_flag device word that is non-zero when the operand holds an inf or NaN (as written by
+ *                trs_split_lo_f32 or through c_flag); NULL = the caller vouches that all values are finite.
+ *   c_lo         when non-NULL, the lo image of C is written alongside C (same layout as C).
+ *   c_flag       device word, zeroed by the caller beforehand, set to 1 when C receives an inf or NaN;
+ *                required with c_lo. */
+typedef struct trs_gemm_planes {
+    const float* a_lo;
+    const float* b_lo;
+    float* c_lo;
+    const uint32_t* a_flag;
+    const uint32_t* b_flag;
+    uint32_t* c_flag;
+} trs_gemm_planes;
+
+/* lo[i] = tf32(src[i] - trunc_tf32(src[i])) for i in [0, count); *flag = 1 when any src[i] is inf / NaN,
+ * else 0.  `src` and `lo` 16-byte aligned for full speed (any alignment works). */
+int32_t trs_split_lo_f32(const float* src, int64_t count, float* lo, uint32_t* flag, trs_stream stream);
+/* trs_matmul_f32 with prepared planes (`planes` may be NULL: identical to trs_matmul_f32).  The result
+ * is bit-identical to the call without planes. */
+int32_t trs_matmul_f32_planes(const trs_gemm_desc* desc, const trs_gemm_planes* planes, trs_stream stream);
+/* What trs_matmul_f32_planes would do with this descriptor (no launch): the algorithm, and whether it
+ * would read a prepared lo image of A / of B (0 when the operand is re-laid or the FP32 kernel runs). */
+int32_t trs_matmul_plan(const trs_gemm_desc* desc, int32_t* algo, int32_t* a_plane_used, int32_t* b_plane_used);
+
+/* ---- the one collective -------------------------------------------------------------------------
+ * New: the reference has no distributed backend (python/torch_rs/distributed/distributed_c10d.py:39-74); a host
+ * keeps its LOCAL_RANK convention (same file, 71-72) to choose `device`.  The data-parallel MLP step sums the
+ * weight gradients of all ranks; everything else on the path shards with no exchange.  NCCL (NVLink / NVSwitch)
+ * is loaded on first use; without it these return TRS_ERR_UNSUPPORTED.
+ *   trs_comm_unique_id   rank 0 fills 128 bytes and hands them to every rank by any means the host has
+ *   trs_comm_init_rank   collective over all ranks; one communicator per rank, bound to `device`
+ *   trs_comm_allreduce_sum_f32  in place, enqueued on `stream` (same device); ordered like any other work on it
+ *   trs_comm_destroy     after the stream has drained */
+int32_t trs_comm_unique_id(char* id128);
+int32_t trs_comm_init_rank(int32_t device, int32_t nranks, int32_t rank, const char* id128, trs_comm* comm);
+int32_t trs_comm_allreduce_sum_f32(trs_comm comm, float* data, int64_t count, trs_stream stream);
+int32_t trs_comm_info(trs_comm comm, int32_t* device, int32_t* nranks, int32_t* rank);
+int32_t trs_comm_destroy(trs_comm comm);
+
 /* ---- diagnostics -------------------------------------------------------------------------------- */
+/* Test aid for the bounded waits of the matmul kernels (no reference counterpart): one warp waits at most
+ * `limit_cycles` SM clocks (<= 1e8) on a barrier that nothing arrives on, through the kernels' own wait loop,
+ * and reports the timeout the way they do -- the next trs_stream_sync / trs_device_sync on the device returns
+ * TRS_ERR_DEVICE_STATUS once.  The kernel returns by itself; nothing traps or spins unbounded. */
+int32_t trs_debug_wait_probe(trs_stream stream, int64_t limit_cycles);
 const char* trs_status_string(int32_t status);
 const char* trs_last_error_message(void);          /* thread-local, valid until the next failing call */
 int64_t trs_kernel_launch_count(void);             /* kernels launched by this library since load */

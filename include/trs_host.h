@@ -52,7 +52,11 @@ int32_t trsh_rank(trsh_tensor t, int32_t* rank);
 int32_t trsh_layout(trsh_tensor t, int64_t* shape, int64_t* strides, int64_t* offset, int64_t* numel);
 int32_t trsh_device(trsh_tensor t, int32_t* device);
 int32_t trsh_flags(trsh_tensor t, int32_t* requires_grad, int32_t* is_leaf, int32_t* is_contiguous, int32_t* is_pending);
-int32_t trsh_data_ptr(trsh_tensor t, void** ptr);         /* forces the value; device address of element 0 */
+/* Storage::data_ptr (src/storage.rs:154): forces the value; device address of element 0.  The holder of the
+ * address may write through it, so from here on the engine reads this storage eagerly and keeps no derived
+ * copies of it; trsh_const_data_ptr is the read-only form without that effect. */
+int32_t trsh_data_ptr(trsh_tensor t, void** ptr);
+int32_t trsh_const_data_ptr(trsh_tensor t, const void** ptr);
 int32_t trsh_shares_storage(trsh_tensor a, trsh_tensor b, int32_t* shared);
 const char* trsh_grad_fn_name(trsh_tensor t);
 
@@ -105,6 +109,24 @@ int32_t trsh_plan_memory_format(int32_t memory_format, int32_t for_clone, int32_
 int32_t trsh_plan_binary(int32_t lrank, const int64_t* lshape, const int64_t* lstrides, int32_t rrank,
                          const int64_t* rshape, const int64_t* rstrides, int32_t* out_rank, int64_t* out_shape,
                          int64_t* out_strides);
+
+/* Operand images for the tensor-core matmul (trs_gemm_planes in trs_cuda.h): kept beside each storage that a
+ * matmul reads, on by default; off = every matmul prepares its operands per call.  trsh_has_operand_image
+ * tells whether `t`'s storage currently carries one. */
+int32_t trsh_set_plane_cache(int32_t on);
+int32_t trsh_has_operand_image(trsh_tensor t, int32_t* has);
+
+/* Data-parallel gradient exchange: the reference has no distributed backend
+ * (python/torch_rs/distributed/distributed_c10d.py:39-74); LOCAL_RANK (71-72) picks the device.  One
+ * communicator per process (trs_comm_* in trs_cuda.h underneath).  trsh_all_reduce_grads sums the .grad of the
+ * given leaves over the ranks in place on a side stream, each one as soon as its own kernel has finished, and
+ * makes the compute stream wait for the last; trsh_all_reduce does the same for one contiguous tensor. */
+int32_t trsh_comm_unique_id(char* id128);
+int32_t trsh_comm_init(int32_t device, int32_t nranks, int32_t rank, const char* id128);
+int32_t trsh_comm_destroy(void);
+int32_t trsh_comm_size(int32_t* nranks);
+int32_t trsh_all_reduce_grads(const trsh_tensor* leaves, int32_t count);
+int32_t trsh_all_reduce(trsh_tensor t);
 
 /* execution control: force pending work of `t` onto the device / wait for the device stream */
 int32_t trsh_materialize(trsh_tensor t);

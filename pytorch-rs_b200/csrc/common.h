@@ -96,6 +96,9 @@ __device__ __forceinline__ void pdl_wait() {
 #endif
 
 int32_t check_stream(trs_stream s);
+// Cached device blocks in stream order (see trs_malloc_async / trs_free_async).
+int32_t malloc_on_stream(trs_stream stream, size_t bytes, void** ptr);
+void free_on_stream(trs_stream stream, void* ptr);
 int sm_count(int device);
 
 }  // namespace trs

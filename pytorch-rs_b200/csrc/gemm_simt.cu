@@ -24,12 +24,19 @@ __device__ __forceinline__ float ref_relu_vjp(float x, float g) {
     return (mag > 0x7f800000u || ((b >> 31) == 0u && mag != 0u)) ? g : 0.0f;
 }
 
+__device__ __forceinline__ bool word_is(const unsigned int* p, unsigned int value) {
+    return p != nullptr && *reinterpret_cast<const volatile unsigned int*>(p) == value;
+}
+__device__ __forceinline__ bool word_set(const unsigned int* p) {
+    return p != nullptr && *reinterpret_cast<const volatile unsigned int*>(p) != 0u;
+}
+
 template <bool A_KFAST, bool B_NFAST>
-__global__ void __launch_bounds__(256, 2) gemm_simt_kernel(const trs_gemm_desc g, const unsigned int* gate, const unsigned int epoch,
+__global__ void __launch_bounds__(256, 2) gemm_simt_kernel(const trs_gemm_desc g, const SimtGate gate, float* c_lo, unsigned int* c_flag,
                                                        const long long tiles_x, const long long tiles_y, const long long total_tiles) {
     pdl_wait();
-    // gated launch: runs only when the preparation of this very call (tagged `epoch`) met an inf / NaN
-    if (gate != nullptr && *reinterpret_cast<const volatile unsigned int*>(gate) != epoch) return;
+    // gated launch: runs only when the preparation of this very call (tagged `epoch`) or a prepared operand image met an inf / NaN
+    if (gate.gated && !word_is(gate.word, gate.epoch) && !word_set(gate.flag_a) && !word_set(gate.flag_b)) return;
     __shared__ __align__(16) float As[2][BK][BM + PAD];
     __shared__ __align__(16) float Bs[2][BK][BN + PAD];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -125,6 +132,20 @@ __global__ void __launch_bounds__(256, 2) gemm_simt_kernel(const trs_gemm_desc g
             if (g.epilogue == TRS_EPI_BIAS_RELU || g.epilogue == TRS_EPI_RELU) v = ref_relu(v);
             if (g.epilogue == TRS_EPI_RELU_VJP) v = ref_relu_vjp(__ldg(aux + idx), v);
             C[idx] = v;
+            if (c_lo) {
+                // lo image of the result for the tensor-core matmul that reads it next: tf32(v - trunc_tf32(v))
+                const unsigned bits = __float_as_uint(v);
+                float lo = 0.0f;
+                if ((bits & 0x7f800000u) == 0x7f800000u) {
+                    *reinterpret_cast<volatile unsigned int*>(c_flag) = 1u;
+                } else {
+                    unsigned l;
+                    const float rest = __fsub_rn(v, __uint_as_float(bits & 0xffffe000u));
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+                    lo = __uint_as_float(l);
+                }
+                c_lo[batch * g.c_batch_stride + idx] = lo;
+            }
         }
     }
   }
@@ -132,27 +153,29 @@ __global__ void __launch_bounds__(256, 2) gemm_simt_kernel(const trs_gemm_desc g
 
 }  // namespace
 
-int32_t gemm_simt_launch(const trs_gemm_desc& g, trs_stream stream, const unsigned int* gate, unsigned int epoch) {
+int32_t gemm_simt_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, trs_stream stream, const SimtGate& gate) {
     const long long tiles_x = (g.n + BN - 1) / BN, tiles_y = (g.m + BM - 1) / BM, total = tiles_x * tiles_y * g.batch;
     // A gated launch almost always returns at once: keep its grid small so that the no-op is cheap.
-    const long long cap = gate ? (long long)sm_count(stream->device) * 2 : (1ll << 31) - 1;
+    const long long cap = gate.gated ? (long long)sm_count(stream->device) * 2 : (1ll << 31) - 1;
     const unsigned grid = (unsigned)std::max<long long>(1, std::min(total, cap));
     const bool a_kfast = g.a_col_stride == 1 || g.a_row_stride != 1;
     const bool b_nfast = g.b_col_stride == 1 || g.b_row_stride != 1;
     auto kernel = a_kfast ? (b_nfast ? gemm_simt_kernel<true, true> : gemm_simt_kernel<true, false>)
                           : (b_nfast ? gemm_simt_kernel<false, true> : gemm_simt_kernel<false, false>);
-    if (gate) {
+    if (gate.gated) {
         // A gated launch sits between tensor-core GEMMs and their preparation kernels: keep their shared-memory
-        // configuration, so that no SM has to drain to switch it for a kernel that returns at once.
-        static std::once_flag once;
-        std::call_once(once, [] {
+        // configuration, so that no SM has to drain to switch it for a kernel that returns at once.  Function
+        // attributes are per device.
+        static std::once_flag once[16];
+        std::call_once(once[stream->device & 15], [] {
             cudaFuncSetAttribute(gemm_simt_kernel<true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(gemm_simt_kernel<true, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(gemm_simt_kernel<false, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(gemm_simt_kernel<false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         });
     }
-    TRS_CUDA(launch_dependent(kernel, dim3(grid), dim3(256), 0, stream->stream, g, gate, epoch, tiles_x, tiles_y, total));
+    TRS_CUDA(launch_dependent(kernel, dim3(grid), dim3(256), 0, stream->stream, g, gate, planes ? planes->c_lo : (float*)nullptr,
+                               planes ? planes->c_flag : (unsigned int*)nullptr, tiles_x, tiles_y, total));
     count_launch();
     return TRS_OK;
 }

@@ -47,8 +47,6 @@ constexpr int TMEM_COLS = 512;                        // two 128x256 FP32 accumu
 constexpr long long WAIT_CYCLES = 2000000000ll;        // bounded waits: about a second of SM clocks
 constexpr int K_PAD = 32;                             // operand planes are padded along K to this many floats
 
-// Error word written by a kernel whose bounded wait ran out (0 = fine).
-__device__ unsigned int g_gemm_error;
 // Written by the split kernels when an operand holds inf/NaN (the split cannot represent those): each
 // tensor-core matmul call owns word (epoch % 8) and marks it with its epoch, so nothing has to be cleared.
 __device__ unsigned int g_nonfinite_seen[8];
@@ -62,14 +60,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Returns false when the wait ran out of iterations.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles) {
     const long long start = clock64();
     for (;;) {
         uint32_t ok;
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        if (clock64() - start > WAIT_CYCLES) return false;
+        if (clock64() - start > limit_cycles) return false;
     }
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
@@ -164,6 +162,18 @@ __device__ __forceinline__ float ref_relu_vjp(float x, float g) {
     return (mag > 0x7f800000u || ((b >> 31) == 0u && mag != 0u)) ? g : 0.0f;
 }
 
+// lo part of the 3-product split for a value the MMA reads in place (hi = the value with its low 13 mantissa
+// bits dropped): lo = tf32(v - hi).  Returns true for inf / NaN, which the split cannot represent (lo = 0).
+__device__ __forceinline__ bool lo_of(float v, float& lo) {
+    const uint32_t bits = __float_as_uint(v);
+    if ((bits & 0x7f800000u) == 0x7f800000u) { lo = 0.0f; return true; }
+    const float rest = __fsub_rn(v, __uint_as_float(bits & 0xffffe000u));      // exact
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    lo = __uint_as_float(l);
+    return false;
+}
+
 struct EpilogueArgs {
     float* c;
     const float* bias;
@@ -175,6 +185,10 @@ struct EpilogueArgs {
     int whole_tiles;      // work items [0, whole_tiles) are complete tiles; each later tile is two half-K items added atomically
     int total_items;
     int a_mn, b_mn;       // pair kernel: the operand's tiles are MN-major (unit stride along its rows) instead of K-major
+    float* c_lo;          // optional: lo image of C (tf32(c - trunc_tf32(c))), laid out like C, for the matmul that reads C next
+    unsigned int* c_flag; // with c_lo: set to 1 when an inf / NaN is stored
+    unsigned int* error;  // word (mapped host memory) that receives the stage number when a bounded wait runs out
+    long long wait_cycles;  // limit of every mbarrier wait, in SM clocks
 };
 
 // Tile order: bands of 16 tile rows, walked column by column, so that the ~148 tiles in flight at
@@ -266,6 +280,21 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_
                     for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
                 }
             }
+            if (e.c_lo && !split) {
+                // lo image of the stored values, for the matmul that consumes C as an operand
+                float l[32];
+                bool nonfinite = false;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) nonfinite |= lo_of(v[j], l[j]);
+                if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.c_lo) & 15u) == 0)) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c_lo + idx0 + j) = make_float4(l[j], l[j + 1], l[j + 2], l[j + 3]);
+                } else {
+                    nonfinite = false;
+                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) { e.c_lo[idx0 + j] = l[j]; nonfinite |= (__float_as_uint(v[j]) & 0x7f800000u) == 0x7f800000u; }
+                }
+                if (nonfinite) *reinterpret_cast<volatile unsigned int*>(e.c_flag) = 1u;
+            }
             if (split) {
                 // half-K partial (plain product only): add onto the zeroed output
                 for (int j = 0; j < 32; ++j) if (col0 + j < e.n) atomicAdd(e.c + idx0 + j, v[j]);
@@ -324,7 +353,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                 decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % STAGES, round = g / STAGES;
-                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1)) { failed = true; break; }
+                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, e.wait_cycles)) { failed = true; break; }
                     const uint32_t full = smem_u32(&full_bar[s]);
                     const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
                     mbar_expect_tx(full, STAGE_BYTES);
@@ -334,7 +363,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                     tma_load_3d(base + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full, kb * BK, tile_n * BN, batch);
                 }
             }
-            if (failed) atomicExch(&g_gemm_error, 1u);
+            if (failed) atomicExch_system(e.error, 1u);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -347,12 +376,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                 decode_item(w, e, t, kb_begin, kb_end, split);
                 const uint32_t acc = it & 1, use = it >> 1;
                 // the epilogue must have drained this accumulator's previous tile
-                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1)) { failed = true; break; }
+                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, e.wait_cycles)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_base + acc * BN;
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % STAGES;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / STAGES) & 1)) { failed = true; break; }
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / STAGES) & 1, e.wait_cycles)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + A_TILE_BYTES);
@@ -369,7 +398,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                 }
                 umma_commit(smem_u32(&acc_full[acc]));                            // accumulator complete (or abandoned)
             }
-            if (failed) atomicExch(&g_gemm_error, 2u);
+            if (failed) atomicExch_system(e.error, 2u);
         }
     } else {
         // ---- epilogue warps 2..5: TMEM lanes 32*(warp%4) .. +31 ----
@@ -384,8 +413,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             decode_item(w, e, t, kb_begin, kb_end, split);
             decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
             const uint32_t acc = it & 1, use = it >> 1;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1)) {
-                if (lane == 0) atomicExch(&g_gemm_error, 3u);
+            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1, e.wait_cycles)) {
+                if (lane == 0) atomicExch_system(e.error, 3u);
                 failed = true;
                 break;
             }
@@ -477,7 +506,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                 const int b_row = tile_n * BN + (int)rank * (BN / 2);
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % PAIR_STAGES, round = g / PAIR_STAGES;
-                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1)) { failed = true; break; }
+                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, e.wait_cycles)) { failed = true; break; }
                     const uint32_t full = map_to_cta(smem_u32(&full_bar[s]), 0);
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
@@ -500,8 +529,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             // stay until the leader's last commits have arrived on this CTA's barriers
             const uint32_t last = g < (uint32_t)PAIR_STAGES ? g : (uint32_t)PAIR_STAGES;
             for (uint32_t u = g - last; u < g && !failed; ++u)
-                if (!mbar_wait(smem_u32(&empty_bar[u % PAIR_STAGES]), (u / PAIR_STAGES) & 1)) failed = true;
-            if (failed) atomicExch(&g_gemm_error, 4u);
+                if (!mbar_wait(smem_u32(&empty_bar[u % PAIR_STAGES]), (u / PAIR_STAGES) & 1, e.wait_cycles)) failed = true;
+            if (failed) atomicExch_system(e.error, 4u);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
@@ -514,12 +543,12 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
                 bool split;
                 decode_item(w, e, t, kb_begin, kb_end, split);
                 const uint32_t acc = it & 1, use = it >> 1;
-                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1)) { failed = true; break; }
+                if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, e.wait_cycles)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_base + acc * BN;
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % PAIR_STAGES;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / PAIR_STAGES) & 1)) { failed = true; break; }
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (g / PAIR_STAGES) & 1, e.wait_cycles)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t base = smem_u32(smem + s * PAIR_STAGE_BYTES);
                     const uint32_t a0 = base, a1 = base + PAIR_A_TILE_BYTES, b0 = base + 2 * PAIR_A_TILE_BYTES, b1 = b0 + PAIR_B_TILE_BYTES;
@@ -543,8 +572,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             // stay until the peer's epilogue has made its last arrivals on this CTA's barriers
             const uint32_t last = it < 2u ? it : 2u;
             for (uint32_t j = it - last; j < it && !failed; ++j)
-                if (!mbar_wait(smem_u32(&acc_empty[j & 1]), (j >> 1) & 1)) failed = true;
-            if (failed) atomicExch(&g_gemm_error, 5u);
+                if (!mbar_wait(smem_u32(&acc_empty[j & 1]), (j >> 1) & 1, e.wait_cycles)) failed = true;
+            if (failed) atomicExch_system(e.error, 5u);
         }
     } else {
         // ---- epilogue warps 2..5 of both CTAs: this CTA's 128 rows of the tile ----
@@ -558,8 +587,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             decode_item(w, e, t, kb_begin, kb_end, split);
             decode_tile<PAIR_GROUP_M>(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
             const uint32_t acc = it & 1, use = it >> 1;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1)) {
-                if (lane == 0) atomicExch(&g_gemm_error, 6u);
+            if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1, e.wait_cycles)) {
+                if (lane == 0) atomicExch_system(e.error, 6u);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -767,9 +796,9 @@ bool mn_major_ok(const float* src, long long batch, long long rows, long long ba
 }
 
 struct DeviceWords {
-    unsigned int* error = nullptr;
+    unsigned int* error = nullptr;       // device-side address of host_error
+    unsigned int* host_error = nullptr;  // page-locked, mapped: kernels write it, the host reads it without a copy
     unsigned int* nonfinite = nullptr;
-    bool launched = false;
     bool smem_set = false;
     unsigned int epoch = 0;     // tag of the latest tensor-core matmul call on this device
     int pair_clusters = 0;      // CTA pairs of the two-CTA kernel that can be resident at once
@@ -783,8 +812,14 @@ int32_t device_words(int device, DeviceWords** out, unsigned int* epoch) {
     if (++w.epoch == 0) ++w.epoch;                       // 0 is the words' initial value: never a tag
     *epoch = w.epoch;
     if (!w.error) {
-        TRS_CUDA(cudaGetSymbolAddress((void**)&w.error, g_gemm_error));
+        unsigned int* host = nullptr;
+        TRS_CUDA(cudaHostAlloc((void**)&host, sizeof(unsigned int), cudaHostAllocMapped | cudaHostAllocPortable));
+        *host = 0;
+        unsigned int* dev = nullptr;
+        if (cudaHostGetDevicePointer((void**)&dev, host, 0) != cudaSuccess) { cudaGetLastError(); cudaFreeHost(host); return fail(TRS_ERR_CUDA, "cannot map the status word"); }
         TRS_CUDA(cudaGetSymbolAddress((void**)&w.nonfinite, g_nonfinite_seen));
+        w.host_error = host;
+        w.error = dev;
     }
     if (!w.smem_set) {
         TRS_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -872,72 +907,167 @@ bool gemm_tc_eligible(const trs_gemm_desc& g) {
     return (double)g.m * (double)g.n * (double)g.k >= (double)(1 << 21);
 }
 
-size_t gemm_tc_scratch_bytes(const trs_gemm_desc& g) {
-    const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
-    return (size_t)(2 * g.batch * (g.m + g.n) * k_pad) * sizeof(float);
+namespace {
+
+// How one operand reaches the MMA.
+struct OperandRoute {
+    bool raw = false;      // K-major, read in place as hi; only a lo image is needed
+    bool mn = false;       // row-contiguous, read in place MN-major (pair kernel); only a lo image is needed
+    bool given = false;    // the caller's lo image is used (raw or mn only)
+    long long floats = 0;  // scratch this operand needs
+};
+
+// Whether a caller's lo image can stand beside the operand: same 16-byte phase as the operand itself.
+bool lo_image_ok(const float* operand, const float* lo) {
+    return lo != nullptr && ((reinterpret_cast<uintptr_t>(lo) & 15u) == (reinterpret_cast<uintptr_t>(operand) & 15u));
 }
 
-// Runs split + GEMM with caller-provided scratch of gemm_tc_scratch_bytes(g).
-int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream stream) {
+void route_operands(const trs_gemm_desc& g, const trs_gemm_planes* p, OperandRoute* ra, OperandRoute* rb) {
+    const bool pair = g.algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
+    const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
+    ra->raw = raw_hi_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
+    rb->raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
+    // An operand that is unit-stride along its rows (a transposed view, or the right operand of a plain A @ B) is
+    // read MN-major as it lies by the pair kernel; only its lo image, in the same order, is needed.
+    // Measured: the MMA reads an MN-major tile 1-3 % slower than a K-major one, while re-laying an operand costs
+    // 4 more bytes of HBM traffic per element; the operand's reuse (the other output extent) decides which is cheaper.
+    ra->mn = pair && kMnMajorOperands && !ra->raw && g.n <= kMnMajorMaxReuse &&
+             mn_major_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
+    rb->mn = pair && kMnMajorOperands && !rb->raw && g.m <= kMnMajorMaxReuse &&
+             mn_major_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
+    ra->given = (ra->raw || ra->mn) && p && lo_image_ok(g.a, p->a_lo);
+    rb->given = (rb->raw || rb->mn) && p && lo_image_ok(g.b, p->b_lo);
+    ra->floats = ra->given ? 0 : (ra->mn ? g.batch * g.k * g.m : (ra->raw ? 1 : 2) * g.batch * g.m * k_pad);
+    rb->floats = rb->given ? 0 : (rb->mn ? g.batch * g.k * g.n : (rb->raw ? 1 : 2) * g.batch * g.n * k_pad);
+}
+
+// Elementwise lo image of a contiguous range (the form a host keeps beside a storage).
+__global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ src, float* __restrict__ lo, long long count,
+                                                       unsigned int* flag, int vec) {
+    bool nonfinite = false;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if (vec) {
+        const long long quads = count >> 2;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += stride) {
+            const float4 t = __ldcs(reinterpret_cast<const float4*>(src) + i);
+            float4 l;
+            nonfinite |= lo_of(t.x, l.x); nonfinite |= lo_of(t.y, l.y); nonfinite |= lo_of(t.z, l.z); nonfinite |= lo_of(t.w, l.w);
+            reinterpret_cast<float4*>(lo)[i] = l;
+        }
+        for (long long i = (quads << 2) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) nonfinite |= lo_of(src[i], lo[i]);
+    } else {
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) nonfinite |= lo_of(__ldg(src + i), lo[i]);
+    }
+    if (nonfinite) *reinterpret_cast<volatile unsigned int*>(flag) = 1u;
+}
+
+// Test aid for the bounded waits: waits, with the given limit, on a barrier that nothing ever arrives on, and
+// reports the timeout through the same error word and host check as the GEMM kernels.  It returns by itself.
+__global__ void wait_probe_kernel(unsigned int* error, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(smem_u32(&bar), 0, limit_cycles)) atomicExch_system(error, 7u);
+    }
+}
+
+}  // namespace
+
+int32_t gemm_tc_plan(const trs_gemm_desc& g, bool* a_image, bool* b_image) {
+    OperandRoute ra, rb;
+    route_operands(g, nullptr, &ra, &rb);
+    *a_image = ra.raw || ra.mn;
+    *b_image = rb.raw || rb.mn;
+    return TRS_OK;
+}
+
+int32_t gemm_split_lo(const float* src, long long count, float* lo, unsigned int* flag, trs_stream stream) {
+    TRS_CUDA(cudaMemsetAsync(flag, 0, sizeof(unsigned int), stream->stream));
+    if (count <= 0) return TRS_OK;
+    const int vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(lo)) & 15u) == 0;
+    const long long items = vec ? (count + 3) / 4 : count;
+    const unsigned grid = (unsigned)std::max<long long>(1, std::min<long long>((items + 255) / 256, (long long)sm_count(stream->device) * 16));
+    split_lo_kernel<<<grid, 256, 0, stream->stream>>>(src, lo, count, flag, vec);
+    TRS_CUDA(cudaGetLastError());
+    count_launch();
+    return TRS_OK;
+}
+
+// Split (where no image was given) + GEMM + the gated exact-FP32 recompute.
+int32_t gemm_tc_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, trs_stream stream) {
+    if (g.m > INT32_MAX || g.n > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "matrix extent above 2^31");
+    if (planes && planes->c_lo && !planes->c_flag) return fail(TRS_ERR_INVALID_ARGUMENT, "c_lo needs c_flag");
     DeviceWords* words = nullptr;
     unsigned int epoch = 0;
     TRS_TRY(device_words(stream->device, &words, &epoch));
     unsigned int* nonfinite = words->nonfinite + (epoch & 7u);
     const long long k_pad = (g.k + K_PAD - 1) / K_PAD * K_PAD;
-    const long long a_plane = g.batch * g.m * k_pad, b_plane = g.batch * g.n * k_pad;
-    float* a_hi = scratch;
-    float* a_lo = a_hi + a_plane;
-    float* b_hi = a_lo + a_plane;
-    float* b_lo = b_hi + b_plane;
-    // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
-    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     const bool pair = g.algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
     const int b_box = pair ? BN / 2 : BN;                // B^T rows one CTA stages
     const int bk = pair ? PAIR_BK : BK;                  // floats along K per pipeline stage
-    bool a_raw = raw_hi_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
-    bool b_raw = raw_hi_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
-    if (a_raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, g.batch > 1 ? g.a_batch_stride : g.m * g.a_row_stride, BM, bk) != TRS_OK) a_raw = false;
-    if (b_raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, g.batch > 1 ? g.b_batch_stride : g.n * g.b_col_stride, b_box, bk) != TRS_OK) b_raw = false;
-    // An operand that is unit-stride along its rows (a transposed view, or the right operand of a plain A @ B) is
-    // read MN-major as it lies by the pair kernel; only its lo plane, in the same [k, rows] order, is prepared.
-    // Measured: the MMA reads an MN-major tile 1-3 % slower than a K-major one, while re-laying an operand costs
-    // 4 more bytes of HBM traffic per element; the operand's reuse (the other output extent) decides which is cheaper.
-    bool a_mn = pair && kMnMajorOperands && !a_raw && g.n <= kMnMajorMaxReuse &&
-                mn_major_ok(g.a, g.batch, g.m, g.a_batch_stride, g.a_row_stride, g.a_col_stride, g.k);
-    bool b_mn = pair && kMnMajorOperands && !b_raw && g.m <= kMnMajorMaxReuse &&
-                mn_major_ok(g.b, g.batch, g.n, g.b_batch_stride, g.b_col_stride, g.b_row_stride, g.k);
-    if (a_mn && make_mn_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_col_stride, g.batch > 1 ? g.a_batch_stride : g.k * g.a_col_stride, BM, bk) != TRS_OK) a_mn = false;
-    if (b_mn && make_mn_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_row_stride, g.batch > 1 ? g.b_batch_stride : g.k * g.b_row_stride, b_box, bk) != TRS_OK) b_mn = false;
-    if (a_mn) {
-        // lo plane [batch, k, m]: the k-fast kernel with the roles of the axes exchanged (its "rows" are k, its "k" is m)
-        TRS_TRY(launch_split(g.a, g.batch, g.k, g.m, g.m, g.a_batch_stride, g.a_col_stride, 1, a_hi, a_lo, nonfinite, epoch, stream, 1));
-        TRS_TRY(make_mn_operand_map(&ma_lo, a_lo, g.m, g.k, g.batch, g.m, g.k * g.m, BM, bk));
-    } else {
-        TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, nonfinite, epoch, stream, a_raw));
-        if (!a_raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
-        TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
+    OperandRoute ra, rb;
+    route_operands(g, planes, &ra, &rb);
+    // A[b, m, k]: rows = m.  B[b, k, n] is consumed as B^T[b, n, k]: rows = n, so its "row stride" is the column stride.
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    const long long a_bs = g.batch > 1 ? g.a_batch_stride : 0, b_bs = g.batch > 1 ? g.b_batch_stride : 0;
+    if (ra.raw && make_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_row_stride, a_bs ? a_bs : g.m * g.a_row_stride, BM, bk) != TRS_OK) ra.raw = ra.given = false;
+    if (rb.raw && make_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_col_stride, b_bs ? b_bs : g.n * g.b_col_stride, b_box, bk) != TRS_OK) rb.raw = rb.given = false;
+    if (ra.mn && make_mn_operand_map(&ma_hi, g.a, g.m, g.k, g.batch, g.a_col_stride, a_bs ? a_bs : g.k * g.a_col_stride, BM, bk) != TRS_OK) ra.mn = ra.given = false;
+    if (rb.mn && make_mn_operand_map(&mb_hi, g.b, g.n, g.k, g.batch, g.b_row_stride, b_bs ? b_bs : g.k * g.b_row_stride, b_box, bk) != TRS_OK) rb.mn = rb.given = false;
+    // The caller's lo image has the operand's own strides: the same map geometry over the other base.
+    if (ra.given && (ra.raw ? make_operand_map(&ma_lo, planes->a_lo, g.m, g.k, g.batch, g.a_row_stride, a_bs ? a_bs : g.m * g.a_row_stride, BM, bk)
+                            : make_mn_operand_map(&ma_lo, planes->a_lo, g.m, g.k, g.batch, g.a_col_stride, a_bs ? a_bs : g.k * g.a_col_stride, BM, bk)) != TRS_OK) ra.given = false;
+    if (rb.given && (rb.raw ? make_operand_map(&mb_lo, planes->b_lo, g.n, g.k, g.batch, g.b_col_stride, b_bs ? b_bs : g.n * g.b_col_stride, b_box, bk)
+                            : make_mn_operand_map(&mb_lo, planes->b_lo, g.n, g.k, g.batch, g.b_row_stride, b_bs ? b_bs : g.k * g.b_row_stride, b_box, bk)) != TRS_OK) rb.given = false;
+    const long long a_floats = ra.given ? 0 : (ra.mn ? g.batch * g.k * g.m : (ra.raw ? 1 : 2) * g.batch * g.m * k_pad);
+    const long long b_floats = rb.given ? 0 : (rb.mn ? g.batch * g.k * g.n : (rb.raw ? 1 : 2) * g.batch * g.n * k_pad);
+    float* scratch = nullptr;
+    if (a_floats + b_floats > 0) TRS_TRY(malloc_on_stream(stream, (size_t)(a_floats + b_floats) * sizeof(float), (void**)&scratch));
+    struct ScratchGuard {       // handed back at once: reuse is ordered behind this stream's work
+        trs_stream s; void* p;
+        ~ScratchGuard() { if (p) free_on_stream(s, p); }
+    } scratch_guard{stream, scratch};
+    // scratch layout: [A lo | A hi (re-laid only)] [B lo | B hi (re-laid only)]
+    float* a_lo = scratch;
+    float* a_hi = a_lo + g.batch * g.m * k_pad;
+    float* b_lo = scratch + a_floats;
+    float* b_hi = b_lo + g.batch * g.n * k_pad;
+    if (!ra.given) {
+        if (ra.mn) {
+            // lo plane [batch, k, m]: the k-fast kernel with the roles of the axes exchanged (its "rows" are k, its "k" is m)
+            TRS_TRY(launch_split(g.a, g.batch, g.k, g.m, g.m, g.a_batch_stride, g.a_col_stride, 1, a_lo, a_lo, nonfinite, epoch, stream, 1));
+            TRS_TRY(make_mn_operand_map(&ma_lo, a_lo, g.m, g.k, g.batch, g.m, g.k * g.m, BM, bk));
+        } else {
+            TRS_TRY(launch_split(g.a, g.batch, g.m, g.k, k_pad, g.a_batch_stride, g.a_row_stride, g.a_col_stride, a_hi, a_lo, nonfinite, epoch, stream, ra.raw));
+            if (!ra.raw) TRS_TRY(make_plane_map(&ma_hi, a_hi, g.m, k_pad, g.batch, BM, bk));
+            TRS_TRY(make_plane_map(&ma_lo, a_lo, g.m, k_pad, g.batch, BM, bk));
+        }
     }
-    if (b_mn) {
-        TRS_TRY(launch_split(g.b, g.batch, g.k, g.n, g.n, g.b_batch_stride, g.b_row_stride, 1, b_hi, b_lo, nonfinite, epoch, stream, 1));
-        TRS_TRY(make_mn_operand_map(&mb_lo, b_lo, g.n, g.k, g.batch, g.n, g.k * g.n, b_box, bk));
-    } else {
-        TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, nonfinite, epoch, stream, b_raw));
-        if (!b_raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
-        TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
+    if (!rb.given) {
+        if (rb.mn) {
+            TRS_TRY(launch_split(g.b, g.batch, g.k, g.n, g.n, g.b_batch_stride, g.b_row_stride, 1, b_lo, b_lo, nonfinite, epoch, stream, 1));
+            TRS_TRY(make_mn_operand_map(&mb_lo, b_lo, g.n, g.k, g.batch, g.n, g.k * g.n, b_box, bk));
+        } else {
+            TRS_TRY(launch_split(g.b, g.batch, g.n, g.k, k_pad, g.b_batch_stride, g.b_col_stride, g.b_row_stride, b_hi, b_lo, nonfinite, epoch, stream, rb.raw));
+            if (!rb.raw) TRS_TRY(make_plane_map(&mb_hi, b_hi, g.n, k_pad, g.batch, b_box, bk));
+            TRS_TRY(make_plane_map(&mb_lo, b_lo, g.n, k_pad, g.batch, b_box, bk));
+        }
     }
     const long long tile_rows = pair ? 2 * BM : BM;
     const long long tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + BN - 1) / BN;
     const long long total_tiles = tiles_m * tiles_n * g.batch;
     if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
     EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / bk), g.epilogue,
-                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles, a_mn ? 1 : 0, b_mn ? 1 : 0};
+                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles, ra.mn ? 1 : 0, rb.mn ? 1 : 0,
+                   planes ? planes->c_lo : nullptr, planes ? planes->c_flag : nullptr, words->error, WAIT_CYCLES};
     // units that work side by side: SMs, or resident CTA pairs
     const long long units = pair ? words->pair_clusters : sm_count(stream->device);
     // A last round that occupies at most half of the units is cut in two along K (plain products on
     // a dense C only): 512 tiles on 148 SMs then take 3.5 instead of 4 tile times.
     const long long tail = total_tiles % units;
     const bool dense_c = g.c_row_stride == g.n && (g.batch == 1 || g.c_batch_stride == g.m * g.n);
-    if (g.epilogue == TRS_EPI_NONE && total_tiles > units && tail > 0 && tail * 2 <= units && e.k_blocks >= 16 && dense_c) {
+    if (g.epilogue == TRS_EPI_NONE && !e.c_lo && total_tiles > units && tail > 0 && tail * 2 <= units && e.k_blocks >= 16 && dense_c) {
         e.whole_tiles = (int)(total_tiles - tail);
         e.total_items = (int)(e.whole_tiles + 2 * tail);
         TRS_CUDA(cudaMemsetAsync(g.c, 0, (size_t)(g.batch * g.m * g.n) * sizeof(float), stream->stream));
@@ -955,34 +1085,43 @@ int32_t gemm_tc_launch_ws(const trs_gemm_desc& g, float* scratch, trs_stream str
         TRS_CUDA(launch_dependent(gemm_tf32x3_kernel, dim3(grid), dim3(192), SMEM_BYTES, stream->stream, ma_hi, ma_lo, mb_hi, mb_lo, e));
     }
     count_launch();
-    words->launched = true;
     // inf / NaN operands: recompute with the exact-FP32 kernel (a no-op launch when none were seen),
     // which keeps the reference's inf/NaN classification of the result.
-    TRS_TRY(gemm_simt_launch(g, stream, nonfinite, epoch));
+    SimtGate gate;
+    gate.word = (ra.given && rb.given) ? nullptr : nonfinite;
+    gate.epoch = epoch;
+    gate.flag_a = ra.given ? planes->a_flag : nullptr;
+    gate.flag_b = rb.given ? planes->b_flag : nullptr;
+    gate.gated = true;
+    TRS_TRY(gemm_simt_launch(g, planes, stream, gate));
     return TRS_OK;
 }
 
-int32_t gemm_tc_launch(const trs_gemm_desc& g, trs_stream stream) {
-    if (g.m > INT32_MAX || g.n > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "matrix extent above 2^31");
-    void* scratch = nullptr;
-    TRS_TRY(trs_malloc(stream->device, gemm_tc_scratch_bytes(g), &scratch));
-    int32_t s = gemm_tc_launch_ws(g, (float*)scratch, stream);
-    trs_free(stream->device, scratch);       // reuse is ordered behind this stream's work
-    return s;
+// Reads (and clears) the error word of kernels with bounded waits; called after a stream or device sync.
+// The word lives in page-locked host memory that the kernels write through a mapped pointer, so the check is a
+// plain host read: any sync on the device sees (once) an error raised by a kernel that has completed.
+int32_t gemm_check_status(int device) {
+    if (device < 0 || device >= 16) return TRS_OK;
+    unsigned int value = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_words_mu);
+        DeviceWords& w = g_words[device];
+        if (!w.host_error) return TRS_OK;
+        value = *reinterpret_cast<volatile unsigned int*>(w.host_error);
+        if (value != 0) *reinterpret_cast<volatile unsigned int*>(w.host_error) = 0;
+    }
+    if (value != 0)
+        return fail(TRS_ERR_DEVICE_STATUS, "tensor-core matmul: a bounded wait ran out (stage %u); the result is invalid", value);
+    return TRS_OK;
 }
 
-// Reads (and clears) the error word of kernels with bounded waits; called after a stream or device sync.
-int32_t gemm_check_status(int device) {
-    DeviceWords& w = g_words[device];
-    if (!w.launched || !w.error) return TRS_OK;
-    unsigned int value = 0;
-    TRS_CUDA(cudaMemcpy(&value, w.error, sizeof value, cudaMemcpyDeviceToHost));
-    w.launched = false;
-    if (value != 0) {
-        unsigned int zero = 0;
-        cudaMemcpy(w.error, &zero, sizeof zero, cudaMemcpyHostToDevice);
-        return fail(TRS_ERR_DEVICE_STATUS, "tensor-core matmul: a bounded wait ran out (stage %u); the result is invalid", value);
-    }
+int32_t gemm_wait_probe(trs_stream stream, long long limit_cycles) {
+    DeviceWords* words = nullptr;
+    unsigned int epoch = 0;
+    TRS_TRY(device_words(stream->device, &words, &epoch));
+    wait_probe_kernel<<<1, 32, 0, stream->stream>>>(words->error, limit_cycles);
+    TRS_CUDA(cudaGetLastError());
+    count_launch();
     return TRS_OK;
 }
 

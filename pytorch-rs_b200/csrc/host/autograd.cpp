@@ -210,6 +210,31 @@ TensorP grad_of(const TensorP& t) {
     return t->meta->grad;
 }
 
+// Moves the parents of a recorded op out of it, so that releasing the op does not release them.
+static void take_parents(const std::shared_ptr<GradFn>& fn, std::vector<std::shared_ptr<AutogradMeta>>& pending) {
+    if (!fn || fn.use_count() != 1) return;
+    for (Edge& e : fn->in)
+        if (e.meta) pending.push_back(std::move(e.meta));
+}
+
+AutogradMeta::~AutogradMeta() {
+    if (grad_ready) trs_event_destroy(grad_ready);
+    // src/tensor.rs:189-206: walk the chain of sole-owned ancestors with a work list instead of letting each
+    // destructor call the next one.
+    std::vector<std::shared_ptr<AutogradMeta>> pending;
+    take_parents(grad_fn, pending);
+    grad_fn.reset();
+    while (!pending.empty()) {
+        std::shared_ptr<AutogradMeta> parent = std::move(pending.back());
+        pending.pop_back();
+        if (parent.use_count() == 1) {
+            take_parents(parent->grad_fn, pending);
+            parent->grad_fn.reset();
+        }
+        // `parent` is released here; it has no parents left, so its own destructor does not descend
+    }
+}
+
 void backward(const TensorP& root) {
     std::lock_guard<std::recursive_mutex> lock(g_engine_mu);
     // src/tensor.rs:884-898
@@ -220,53 +245,60 @@ void backward(const TensorP& root) {
     const int device = root->device();
     NoGrad guard;
 
-    // Topology first (src/tensor.rs:2945-2994): every node reachable from the root, with the
-    // number of consumers that will send it a gradient; a freed value-dependent node aborts
-    // before anything runs.
-    std::vector<AutogradMeta*> order;
-    std::unordered_map<AutogradMeta*, int> pending;
-    std::unordered_map<AutogradMeta*, std::shared_ptr<AutogradMeta>> owner;
+    // Topology first (collect_topology, src/tensor.rs:2945-2994): depth-first from the root, the first input of a
+    // node explored first, every node listed after all of its inputs; a freed value-dependent node aborts before
+    // anything runs.  The nodes are then processed in the reverse of that list, as the reference does, so that
+    // several contributions to one tensor are added in the reference's order.
+    std::vector<std::shared_ptr<AutogradMeta>> topology;
     {
-        std::vector<std::shared_ptr<AutogradMeta>> stack{root->meta};
-        std::unordered_set<AutogradMeta*> seen{root->meta.get()};
+        struct Frame { std::shared_ptr<AutogradMeta> meta; bool exit; };
+        std::vector<Frame> stack{{root->meta, false}};
+        std::unordered_set<AutogradMeta*> seen;
         while (!stack.empty()) {
-            auto m = stack.back();
+            Frame f = std::move(stack.back());
             stack.pop_back();
-            owner[m.get()] = m;
-            order.push_back(m.get());
-            if (m->leaf) continue;
-            if (m->freed || !m->grad_fn) throw Error(ErrKind::BackwardGraphFreed, kFreedMessage);
-            for (const Edge& e : m->grad_fn->in) {
-                if (!e.meta) continue;
-                pending[e.meta.get()] += 1;
-                if (seen.insert(e.meta.get()).second) stack.push_back(e.meta);
-            }
+            if (f.exit) { topology.push_back(std::move(f.meta)); continue; }
+            if (!seen.insert(f.meta.get()).second) continue;
+            if (!f.meta->leaf && (f.meta->freed || !f.meta->grad_fn)) throw Error(ErrKind::BackwardGraphFreed, kFreedMessage);
+            stack.push_back({f.meta, true});
+            if (f.meta->leaf) continue;
+            const std::vector<Edge>& in = f.meta->grad_fn->in;
+            for (size_t i = in.size(); i-- > 0;)            // pushed last = explored first
+                if (in[i].meta) stack.push_back({in[i].meta, false});
         }
     }
 
     std::unordered_map<AutogradMeta*, TensorP> grads;
     grads[root->meta.get()] = full(root->v.shape, 1.0f, device);
-    std::vector<AutogradMeta*> ready{root->meta.get()};
     std::vector<std::pair<AutogradMeta*, TensorP>> leaf_grads;
     std::vector<AutogradMeta*> visited_nodes;
-    while (!ready.empty()) {
-        AutogradMeta* m = ready.back();
-        ready.pop_back();
-        TensorP g = grads[m];
-        grads.erase(m);
+    for (size_t pos = topology.size(); pos-- > 0;) {
+        AutogradMeta* m = topology[pos].get();
+        if (!m->leaf) visited_nodes.push_back(m);           // its saved values are consumed whether or not a gradient reaches it
+        auto found = grads.find(m);
+        if (found == grads.end()) continue;                 // nothing flowed here
+        TensorP g = found->second;
+        grads.erase(found);
         if (m->leaf) {
-            if (g) leaf_grads.emplace_back(m, g);
+            // Every contribution to this leaf has been recorded: run its kernels now rather than at the end, so
+            // that a gradient exchange on another stream can start under the rest of the backward pass.
+            if (!layout_is_contiguous(g->v.shape, g->v.strides)) g = contiguous(g);
+            if (!m->grad && !g->v.st->node && g->v.st.use_count() > 1) g = contiguous_result(TRS_OP_COPY, {g->v}, g->v.shape, device);
+            materialize(g->v.st);
+            if (!m->grad) {
+                if (!m->grad_ready) check_cuda(trs_event_create(&m->grad_ready), "creating the gradient event");
+                check_cuda(trs_event_record(m->grad_ready, stream_for(device)), "recording the gradient event");
+            }
+            leaf_grads.emplace_back(m, g);
             continue;
         }
-        visited_nodes.push_back(m);
         const GradFn& fn = *m->grad_fn;
-        std::vector<TensorP> contributions;
-        if (g) contributions = apply(fn, g, device);
+        std::vector<TensorP> contributions = apply(fn, g, device);
         for (size_t i = 0; i < fn.in.size(); ++i) {
             AutogradMeta* target = fn.in[i].meta.get();
-            if (!target) continue;
-            if (g && contributions[i]) grads[target] = accumulate(grads.count(target) ? grads[target] : nullptr, contributions[i], device);
-            if (--pending[target] == 0) ready.push_back(target);
+            if (!target || !contributions[i]) continue;
+            auto have = grads.find(target);
+            grads[target] = accumulate(have == grads.end() ? nullptr : have->second, contributions[i], device);
         }
     }
 
@@ -276,16 +308,14 @@ void backward(const TensorP& root) {
     for (auto& lg : leaf_grads) {
         AutogradMeta* leaf = lg.first;
         TensorP g = lg.second;
-        if (!layout_is_contiguous(g->v.shape, g->v.strides)) g = contiguous(g);
         if (!leaf->grad) {
-            // Own the values: copy unless this is a fresh result nobody else holds.
-            if (!g->v.st->node && g->v.st.use_count() > 1) g = contiguous_result(TRS_OP_COPY, {g->v}, g->v.shape, device);
-            materialize(g->v.st);
+            mark_written_in_place(*g->v.st);                  // later backward passes add into it
             leaf->grad = make_tensor(View{g->v.st, leaf->leaf_shape, contiguous_strides(leaf->leaf_shape), g->v.offset});
         } else {
-            materialize(g->v.st);
             check_cuda(trs_accumulate_f32(leaf->grad->v.st->ptr + leaf->grad->v.offset, g->v.st->ptr + g->v.offset, leaf->grad->numel,
                                           stream_for(device)), "leaf gradient accumulation");
+            if (!leaf->grad_ready) check_cuda(trs_event_create(&leaf->grad_ready), "creating the gradient event");
+            check_cuda(trs_event_record(leaf->grad_ready, stream_for(device)), "recording the gradient event");
         }
     }
     for (AutogradMeta* m : visited_nodes)

@@ -91,6 +91,14 @@ int32_t trsh_data_ptr(trsh_tensor t, void** ptr) {
     return guarded([&] {
         const Tensor& x = *get(t);
         materialize(x.v.st);
+        mark_written_in_place(*x.v.st);      // whoever holds the address may write through it
+        *ptr = x.v.st->ptr + x.v.offset;
+    });
+}
+int32_t trsh_const_data_ptr(trsh_tensor t, const void** ptr) {
+    return guarded([&] {
+        const Tensor& x = *get(t);
+        materialize(x.v.st);
         *ptr = x.v.st->ptr + x.v.offset;
     });
 }
@@ -193,6 +201,24 @@ int32_t trsh_plan_binary(int32_t lrank, const int64_t* lshape, const int64_t* ls
         std::copy(strides.begin(), strides.end(), out_strides);
     });
 }
+
+int32_t trsh_set_plane_cache(int32_t on) { return guarded([&] { set_plane_cache(on != 0); }); }
+int32_t trsh_has_operand_image(trsh_tensor t, int32_t* has) { return guarded([&] { *has = get(t)->v.st->lo != nullptr; }); }
+
+int32_t trsh_comm_unique_id(char* id128) { return guarded([&] { comm_unique_id(id128); }); }
+int32_t trsh_comm_init(int32_t device, int32_t nranks, int32_t rank, const char* id128) {
+    return guarded([&] { comm_init(device, nranks, rank, id128); });
+}
+int32_t trsh_comm_destroy(void) { return guarded([&] { comm_destroy(); }); }
+int32_t trsh_comm_size(int32_t* nranks) { return guarded([&] { *nranks = comm_size(); }); }
+int32_t trsh_all_reduce_grads(const trsh_tensor* leaves, int32_t count) {
+    return guarded([&] {
+        std::vector<TensorP> v;
+        for (int32_t i = 0; i < count; ++i) v.push_back(get(leaves[i]));
+        all_reduce_grads(v);
+    });
+}
+int32_t trsh_all_reduce(trsh_tensor t) { return guarded([&] { all_reduce_tensor(get(t)); }); }
 
 int32_t trsh_materialize(trsh_tensor t) { return guarded([&] { materialize(get(t)->v.st); }); }
 int32_t trsh_sync(int32_t device) { return guarded([&] { sync(device); }); }

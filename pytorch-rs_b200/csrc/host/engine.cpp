@@ -18,7 +18,7 @@ std::recursive_mutex g_engine_mu;
 
 namespace {
 thread_local int t_no_grad_depth = 0;
-std::map<int, trs_stream> g_streams;
+std::map<int, trs_stream>& g_streams = *new std::map<int, trs_stream>();   // never destroyed: storages may outlive static teardown
 }  // namespace
 
 bool grad_enabled() { return t_no_grad_depth == 0; }   // src/grad_mode.rs:5-56
@@ -42,8 +42,65 @@ trs_stream stream_for(int device) {
     return s;
 }
 
+namespace {
+bool g_plane_cache = true;
+}
+void set_plane_cache(bool on) { g_plane_cache = on; }
+bool plane_cache_enabled() { return g_plane_cache; }
+
+// Blocks come from and go back to the device cache in the order of the engine's compute stream: a block freed
+// here may still be read by kernels already queued on that stream, and the cache hands it to another stream
+// only behind that work.
+float* alloc_floats(i64 count, int device) {
+    void* p = nullptr;
+    int32_t s = trs_malloc_async(device, (size_t)std::max<i64>(count, 1) * sizeof(float), stream_for(device), &p);
+    if (s == TRS_ERR_ALLOCATION_FAILED)
+        throw Error(ErrKind::AllocationFailed, "failed to allocate storage for " + std::to_string(count) + " elements");
+    check_cuda(s, "device allocation");
+    return (float*)p;
+}
+
+void free_floats(int device, void* ptr) {
+    if (!ptr) return;
+    auto it = g_streams.find(device);
+    if (it != g_streams.end()) trs_free_async(device, ptr, it->second);
+    else trs_free(device, ptr);
+}
+
 Storage::~Storage() {
-    if (ptr) trs_free(device, ptr);
+    free_floats(device, ptr);
+    free_floats(device, lo);         // the flag word lives in the same block
+}
+
+void mark_written_in_place(Storage& st) {
+    st.written_in_place = true;
+    if (st.lo) {                      // an image of values that may now change is worthless
+        free_floats(st.device, st.lo);
+        st.lo = nullptr;
+        st.lo_flag = nullptr;
+    }
+}
+
+// One block: `count` floats of lo values, then (512-byte aligned) the inf/NaN word.
+void alloc_lo_image(Storage& st) {
+    const i64 padded = (st.count + 127) / 128 * 128;
+    float* block = alloc_floats(padded + 128, st.device);
+    st.lo = block;
+    st.lo_flag = reinterpret_cast<uint32_t*>(block + padded);
+    check_cuda(trs_fill_f32(block + padded, 1, 0.0f, stream_for(st.device)), "clearing the operand flag");
+}
+
+bool ensure_lo_image(Storage& st, i64 view_numel) {
+    if (st.lo) return true;
+    // not for values that may change, nor for a small window of a large buffer
+    if (!g_plane_cache || st.written_in_place || st.node || !st.ptr || st.count == 0 || view_numel * 64 < st.count) return false;
+    const i64 padded = (st.count + 127) / 128 * 128;
+    float* block = alloc_floats(padded + 128, st.device);
+    int32_t s = trs_split_lo_f32(st.ptr, st.count, block, reinterpret_cast<uint32_t*>(block + padded), stream_for(st.device));
+    if (s != TRS_OK) { free_floats(st.device, block); check_cuda(s, "operand image"); }
+    st.lo = block;
+    st.lo_flag = reinterpret_cast<uint32_t*>(block + padded);
+    return true;
 }
 
 namespace {
@@ -91,12 +148,7 @@ static std::shared_ptr<Storage> alloc_storage(i64 count, int device) {
     auto st = std::make_shared<Storage>();
     st->device = device;
     st->count = count;
-    void* p = nullptr;
-    int32_t s = trs_malloc(device, (size_t)std::max<i64>(count, 1) * sizeof(float), &p);
-    if (s == TRS_ERR_ALLOCATION_FAILED)
-        throw Error(ErrKind::AllocationFailed, "failed to allocate storage for " + std::to_string(count) + " elements");
-    check_cuda(s, "device allocation");
-    st->ptr = (float*)p;
+    st->ptr = alloc_floats(count, device);
     return st;
 }
 
@@ -203,11 +255,16 @@ TensorP pointwise_node(int op, float imm, std::vector<View> args, const Shape& s
     }
     node->n_instr = instrs;
     node->n_leaf = leaves;
+    bool reads_mutable = false;
+    for (const View& a : args) reads_mutable |= a.st->written_in_place;
     node->args = std::move(args);
     auto st = std::make_shared<Storage>();
     st->device = device;
     st->count = element_count(shape);
     st->node = node;
+    // The reference computes every result at once.  Deferring is invisible only while the operands cannot change:
+    // a value that may be written in place later (an accumulating leaf gradient, an exported buffer) is read now.
+    if (reads_mutable) materialize(st);
     return make_tensor(View{st, shape, strides, 0});
 }
 

@@ -66,6 +66,15 @@ struct Storage {
     float* ptr = nullptr;
     i64 count = 0;
     std::shared_ptr<Node> node;   // non-null while the values are still an unevaluated expression
+    // Set once something may write the values in place after construction (a leaf gradient that is accumulated
+    // into, a buffer handed out through data_ptr / DLPack, the target of an all-reduce).  Such a storage is never
+    // a leaf of a pending expression (readers run at record time) and never gets a cached lo image.
+    bool written_in_place = false;
+    // Cached operand image for the tensor-core matmul: lo[i] = tf32(ptr[i] - trunc_tf32(ptr[i])) for the whole
+    // storage, and a device word that is non-zero when the storage holds an inf / NaN.  The values of a storage
+    // never change (src/storage.rs:7-18), so the image is computed at most once and dies with the storage.
+    float* lo = nullptr;
+    uint32_t* lo_flag = nullptr;
     ~Storage();
 };
 
@@ -95,6 +104,12 @@ struct AutogradMeta {
     std::shared_ptr<Tensor> grad;             // leaf: accumulated gradient (contiguous)
     Shape leaf_shape;
     int device = 0;
+    // leaf: recorded on the compute stream right behind the kernel that produced the latest gradient, so that a
+    // gradient all-reduce on another stream can start while the rest of the backward pass still runs
+    trs_event grad_ready = nullptr;
+    // Releases a chain of recorded ops with a loop, not by recursion (the reference's iterative Drop,
+    // src/tensor.rs:189-206): a 100,000-op chain must not overflow the stack when its last handle goes.
+    ~AutogradMeta();
 };
 
 struct Tensor {
@@ -136,7 +151,17 @@ TensorP full(const Shape& shape, float value, int device);
 void to_host(const Tensor& t, float* out);                 // logical row-major order
 void to_host_async(const std::shared_ptr<Tensor>& t, float* out);   // pinned destination; valid after sync(device)
 float item(const Tensor& t);
-void materialize(const std::shared_ptr<Storage>& st);
+// `for_matmul`: the value is about to be read as a matmul operand; a matmul that produces it also writes its lo image.
+void materialize(const std::shared_ptr<Storage>& st, bool for_matmul = false);
+// Device blocks in the order of the engine's stream.
+float* alloc_floats(i64 count, int device);
+void free_floats(int device, void* ptr);
+// The cached lo image of a storage (computed on first use); false when the storage does not qualify.
+bool ensure_lo_image(Storage& st, i64 view_numel);
+void alloc_lo_image(Storage& st);                  // empty image + cleared flag, to be filled by a matmul epilogue
+void set_plane_cache(bool on);
+bool plane_cache_enabled();
+void mark_written_in_place(Storage& st);
 void sync(int device);
 
 TensorP permute(const TensorP& t, const std::vector<i64>& dims, int node_kind);
@@ -160,6 +185,17 @@ TensorP sum(const TensorP& t);
 TensorP set_requires_grad(const TensorP& t, bool on);
 void backward(const TensorP& root);
 TensorP grad_of(const TensorP& t);
+
+// Data-parallel gradient exchange (comm.cpp): one NCCL communicator per process.
+void comm_unique_id(char* id128);
+void comm_init(int device, int nranks, int rank, const char* id128);
+void comm_destroy();
+int comm_size();
+// Sums the gradients of the given leaves over all ranks, in place, on a side stream: each all-reduce starts as
+// soon as that gradient's kernel has finished, under the rest of the backward pass; the compute stream waits
+// for the last one.
+void all_reduce_grads(const std::vector<TensorP>& leaves);
+void all_reduce_tensor(const TensorP& t);
 
 // Internal helpers shared with autograd.cpp
 TensorP make_tensor(View v);

@@ -29,14 +29,7 @@ trs_operand operand_of(float* base, i64 offset, const Shape& shape, const Shape&
     return op;
 }
 
-float* alloc_values(Storage& st) {
-    void* p = nullptr;
-    int32_t s = trs_malloc(st.device, (size_t)std::max<i64>(st.count, 1) * sizeof(float), &p);
-    if (s == TRS_ERR_ALLOCATION_FAILED)
-        throw Error(ErrKind::AllocationFailed, "failed to allocate storage for " + std::to_string(st.count) + " elements");
-    check_cuda(s, "device allocation");
-    return (float*)p;
-}
+float* alloc_values(Storage& st) { return alloc_floats(st.count, st.device); }
 
 // ---- matmul ---------------------------------------------------------------------------------------
 
@@ -47,11 +40,12 @@ struct Epilogue {
     float* preact = nullptr;
 };
 
-void run_matmul(Node& mm, float* c, const Epilogue& epi, int device) {
+// `out`: the storage that receives C; when `out_image` is set the matmul also writes C's lo image into it.
+void run_matmul(Node& mm, float* c, const Epilogue& epi, int device, Storage* out = nullptr, bool out_image = false) {
     View& a = mm.args[0];
     View& b = mm.args[1];
-    if (a.st->node) materialize(a.st);
-    if (b.st->node) materialize(b.st);
+    if (a.st->node) materialize(a.st, true);
+    if (b.st->node) materialize(b.st, true);
     const bool batched = mm.shape.size() == 3;
     trs_gemm_desc d{};
     d.batch = batched ? mm.shape[0] : 1;
@@ -75,7 +69,25 @@ void run_matmul(Node& mm, float* c, const Epilogue& epi, int device) {
     d.preact = epi.preact;
     d.epilogue = epi.kind;
     d.algo = TRS_GEMM_AUTO;
-    check_cuda(trs_matmul_f32(&d, stream_for(device)), "matmul");
+    // Operand images: a storage's lo values are computed once and kept beside it, so a weight, an activation that
+    // feeds both a forward and a backward product, or any operand used twice is prepared once, not per call.
+    trs_gemm_planes planes{};
+    int32_t algo = 0, a_used = 0, b_used = 0;
+    check_cuda(trs_matmul_plan(&d, &algo, &a_used, &b_used), "matmul");
+    i64 a_numel = 1, b_numel = 1;
+    for (i64 e : a.shape) a_numel *= e;
+    for (i64 e : b.shape) b_numel *= e;
+    if (a_used && ensure_lo_image(*a.st, a_numel)) { planes.a_lo = a.st->lo + a.offset; planes.a_flag = a.st->lo_flag; }
+    if (b_used && ensure_lo_image(*b.st, b_numel)) { planes.b_lo = b.st->lo + b.offset; planes.b_flag = b.st->lo_flag; }
+    const bool tensor_core = algo == TRS_GEMM_TCGEN05_3XTF32 || algo == TRS_GEMM_TCGEN05_3XTF32_2CTA;
+    if (out && out_image && tensor_core && plane_cache_enabled() && !out->lo) {
+        alloc_lo_image(*out);
+        planes.c_lo = out->lo;
+        planes.c_flag = out->lo_flag;
+    }
+    int32_t status = trs_matmul_f32_planes(&d, &planes, stream_for(device));
+    if (status != TRS_OK && planes.c_lo) { free_floats(device, out->lo); out->lo = nullptr; out->lo_flag = nullptr; }
+    check_cuda(status, "matmul");
 }
 
 bool is_pending_matmul(const View& v) { return v.st->node && v.st->node->op == OP_MATMUL; }
@@ -93,7 +105,7 @@ bool is_column_bias(const View& v, const Shape& out_shape) {
 long external_holders(const std::shared_ptr<Storage>& st) { return st.use_count() - 1; }
 
 // Tries the fused-epilogue forms with `root` as the outermost node.  Returns true when it ran.
-bool try_fused_matmul(const std::shared_ptr<Storage>& root) {
+bool try_fused_matmul(const std::shared_ptr<Storage>& root, bool for_matmul) {
     Node& r = *root->node;
     if (r.strides != contiguous_strides(r.shape) || r.shape.size() < 2) return false;
     const int device = root->device;
@@ -110,7 +122,7 @@ bool try_fused_matmul(const std::shared_ptr<Storage>& root) {
     if (bias_add(r, &mm, &bias)) {                                         // X @ W + b
         float* c = alloc_values(*root);
         Epilogue e; e.kind = TRS_EPI_BIAS; e.bias = bias->st->ptr + bias->offset;
-        run_matmul(*mm->st->node, c, e, device);
+        run_matmul(*mm->st->node, c, e, device, root.get(), for_matmul);
         root->ptr = c; root->node.reset();
         return true;
     }
@@ -119,7 +131,7 @@ bool try_fused_matmul(const std::shared_ptr<Storage>& root) {
         if (is_pending_matmul(inner) && external_holders(inner.st) == 0) {   // relu(X @ W)
             float* c = alloc_values(*root);
             Epilogue e; e.kind = TRS_EPI_RELU;
-            run_matmul(*inner.st->node, c, e, device);
+            run_matmul(*inner.st->node, c, e, device, root.get(), for_matmul);
             root->ptr = c; root->node.reset();
             return true;
         }
@@ -131,7 +143,7 @@ bool try_fused_matmul(const std::shared_ptr<Storage>& root) {
             float* pre = nullptr;
             if (keep_preact) { pre = alloc_values(*inner.st); e.preact = pre; }
             std::shared_ptr<Storage> inner_st = inner.st;
-            run_matmul(*mm->st->node, c, e, device);
+            run_matmul(*mm->st->node, c, e, device, root.get(), for_matmul);
             if (keep_preact) { inner_st->ptr = pre; inner_st->node.reset(); }
             root->ptr = c; root->node.reset();
             return true;
@@ -144,7 +156,8 @@ bool try_fused_matmul(const std::shared_ptr<Storage>& root) {
             z.strides == r.strides) {
             float* c = alloc_values(*root);
             Epilogue e; e.kind = TRS_EPI_RELU_VJP; e.aux = z.st->ptr + z.offset;
-            run_matmul(*g.st->node, c, e, device);
+            // dZ of a linear layer: its next reader is the weight-gradient product X^T @ dZ, so its image is written now
+            run_matmul(*g.st->node, c, e, device, root.get(), true);
             root->ptr = c; root->node.reset();
             return true;
         }
@@ -180,18 +193,18 @@ void collect(Storage* s, Dag& dag) {
 
 }  // namespace
 
-void materialize(const std::shared_ptr<Storage>& root) {
+void materialize(const std::shared_ptr<Storage>& root, bool for_matmul) {
     std::lock_guard<std::recursive_mutex> lock(g_engine_mu);
     if (!root->node) return;
     const int device = root->device;
     if (root->node->op == OP_MATMUL) {
         float* c = alloc_values(*root);
-        run_matmul(*root->node, c, Epilogue{}, device);
+        run_matmul(*root->node, c, Epilogue{}, device, root.get(), for_matmul);
         root->ptr = c;
         root->node.reset();
         return;
     }
-    if (try_fused_matmul(root)) return;
+    if (try_fused_matmul(root, for_matmul)) return;
 
     for (int attempt = 0; attempt < 64; ++attempt) {
         Dag dag;
@@ -258,7 +271,7 @@ void materialize(const std::shared_ptr<Storage>& root) {
         }
         int32_t status = trs_pointwise(&prog, ins.data(), outs.data(), stream_for(device));
         if (status != TRS_OK) {
-            for (float* b : bufs) trs_free(device, b);
+            for (float* b : bufs) free_floats(device, b);
             check_cuda(status, "fused pointwise kernel");
         }
         // Commit: extras first (the root's expression still references them), the root last,

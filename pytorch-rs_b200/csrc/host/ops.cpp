@@ -159,6 +159,7 @@ TensorP matmul(const TensorP& l, const TensorP& r) {
     st->device = l->device();
     st->count = element_count(shape);
     st->node = node;
+    if (l->v.st->written_in_place || r->v.st->written_in_place) materialize(st);   // operands that may change are read now
     TensorP out = make_tensor(View{st, shape, node->strides, 0});
     if ((l->requires_grad() || r->requires_grad()) && grad_enabled())
         record(out, GK::Matmul, shape.size() == 3 ? "BmmBackward0" : "MmBackward0", {l.get(), r.get()},

@@ -11,6 +11,8 @@
 #include <algorithm>
 #include <vector>
 
+#include <atomic>
+
 #include "common.h"
 #include "reduce.h"
 
@@ -189,13 +191,19 @@ int32_t reduce_sum_ws(const trs_operand* input, float* out, float* scratch, int 
     return TRS_OK;
 }
 
-void colsum_geometry(int device, long long rows, long long cols, int* chunks, long long* rows_per_chunk) {
+void colsum_geometry_for(int sms, long long rows, long long cols, long long max_partials, int* chunks, long long* rows_per_chunk) {
     long long col_tiles = (cols + 127) / 128;
-    long long want = std::max<long long>(1, ((long long)sm_count(device) * 4) / col_tiles);
+    long long want = std::max<long long>(1, ((long long)sms * 4) / col_tiles);
     long long c = std::min<long long>(want, std::max<long long>(1, rows / 64));
     c = std::min<long long>(c, 1024);
+    // a bounded partials buffer (the allocation-free entry point) caps the number of row chunks
+    if (max_partials > 0) c = std::min<long long>(c, std::max<long long>(1, max_partials / std::max<long long>(cols, 1)));
     *rows_per_chunk = (rows + c - 1) / c;
     *chunks = (int)((rows + *rows_per_chunk - 1) / *rows_per_chunk);
+}
+
+void colsum_geometry(int device, long long rows, long long cols, int* chunks, long long* rows_per_chunk) {
+    colsum_geometry_for(sm_count(device), rows, cols, 0, chunks, rows_per_chunk);
 }
 
 int32_t unbroadcast_sum_ws(const float* input, long long rows, long long cols, int by_rows, float* out, float* scratch,
@@ -239,9 +247,9 @@ int32_t trs_reduce_sum_f32(const trs_operand* input, float* out, trs_stream stre
     for (int a = 0; a < input->rank; ++a) n *= input->shape[a];
     const int need = sum_partials_needed(stream->device, std::max<long long>(n, 1));
     void* scratch = nullptr;
-    TRS_TRY(trs_malloc(stream->device, (size_t)need * sizeof(float), &scratch));
+    TRS_TRY(malloc_on_stream(stream, (size_t)need * sizeof(float), &scratch));
     int32_t s = reduce_sum_ws(input, out, (float*)scratch, need, stream);
-    trs_free(stream->device, scratch);   // reuse is ordered behind this stream's work
+    free_on_stream(stream, scratch);     // reuse is ordered behind this stream's work
     return s;
 }
 
@@ -258,10 +266,10 @@ int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, 
         long long rpc = 0;
         colsum_geometry(stream->device, rows, cols, &chunks, &rpc);
         floats = (long long)chunks * cols;
-        TRS_TRY(trs_malloc(stream->device, (size_t)floats * sizeof(float), &scratch));
+        TRS_TRY(malloc_on_stream(stream, (size_t)floats * sizeof(float), &scratch));
     }
     int32_t s = unbroadcast_sum_ws(input, rows, cols, by_rows, out, (float*)scratch, floats, stream);
-    if (scratch) trs_free(stream->device, scratch);
+    if (scratch) free_on_stream(stream, scratch);
     return s;
 }
 
@@ -274,12 +282,12 @@ int32_t trs_unbroadcast_sum_f32(const float* input, int64_t rows, int64_t cols, 
 // the process exits.
 constexpr long long kNoAllocScratchFloats = 262144;      // 1 MiB; also the largest `cols` accepted
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
-static float* g_noalloc_scratch_ptr[16];                  // device address per device, resolved once
+static std::atomic<float*> g_noalloc_scratch_ptr[16];     // device address per device, resolved once
 
 int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, float* out, trs_stream stream) {
     TRS_TRY(check_stream(stream));
     if (rows < 0 || cols < 0) return fail(TRS_ERR_INVALID_ARGUMENT, "negative extent");
-    if (!out || (!input && rows * cols != 0)) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (!out || (!input && rows != 0 && cols != 0)) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL argument");
     if (cols > kNoAllocScratchFloats)
         return fail(TRS_ERR_UNSUPPORTED, "trs_colsum_f32_noalloc: %lld columns exceed the fixed scratch of %lld floats; "
                                          "use trs_unbroadcast_sum_f32", (long long)cols, kNoAllocScratchFloats);
@@ -289,22 +297,17 @@ int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, f
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     if (cols == 0) return TRS_OK;
     // The array's name is only a host-side handle; the kernels need its address on THIS device.
-    if (!g_noalloc_scratch_ptr[device]) {
-        float* ptr = nullptr;
-        cudaError_t err = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    float* scratch = g_noalloc_scratch_ptr[device].load(std::memory_order_acquire);
+    if (!scratch) {
+        cudaError_t err = cudaGetSymbolAddress((void**)&scratch, g_noalloc_scratch);
         if (err != cudaSuccess) return cuda_fail(err, "cudaGetSymbolAddress(g_noalloc_scratch)");
-        g_noalloc_scratch_ptr[device] = ptr;
+        g_noalloc_scratch_ptr[device].store(scratch, std::memory_order_release);   // every thread resolves the same address
     }
-    float* scratch = g_noalloc_scratch_ptr[device];
     if (rows == 0) { fill_value_async(out, cols, 0.0f, stream); return TRS_OK; }
     int chunks = 0;
     long long rows_per_chunk = 0;
-    colsum_geometry(device, rows, cols, &chunks, &rows_per_chunk);
-    const long long fit = kNoAllocScratchFloats / cols;       // >= 1 because cols <= the scratch size
-    if (chunks > fit) {
-        rows_per_chunk = (rows + fit - 1) / fit;
-        chunks = (int)((rows + rows_per_chunk - 1) / rows_per_chunk);
-    }
+    // as many row chunks as the grid wants, but never more partials than the fixed array holds
+    colsum_geometry_for(sm_count(device), rows, cols, kNoAllocScratchFloats, &chunks, &rows_per_chunk);
     const int vec = (cols % 4 == 0) && (((uintptr_t)input & 15u) == 0);
     dim3 grid((unsigned)((cols + 127) / 128), (unsigned)chunks);
     // Stage 1 writes every partial that stage 2 reads, so nothing left by an earlier call matters.
@@ -312,6 +315,17 @@ int32_t trs_colsum_f32_noalloc(const float* input, int64_t rows, int64_t cols, f
     colsum_stage2<<<(unsigned)((cols + kBlock - 1) / kBlock), kBlock, 0, stream->stream>>>(scratch, chunks, cols, out);
     TRS_CUDA(cudaGetLastError());
     count_launch(2);
+    return TRS_OK;
+}
+
+int32_t trs_colsum_noalloc_geometry(int32_t sm_count, int64_t rows, int64_t cols, int32_t* chunks, int64_t* rows_per_chunk) {
+    if (sm_count < 1 || rows < 1 || cols < 1 || cols > kNoAllocScratchFloats || !chunks || !rows_per_chunk)
+        return fail(TRS_ERR_INVALID_ARGUMENT, "bad trs_colsum_noalloc_geometry arguments");
+    int c = 0;
+    long long rpc = 0;
+    colsum_geometry_for(sm_count, rows, cols, kNoAllocScratchFloats, &c, &rpc);
+    *chunks = c;
+    *rows_per_chunk = rpc;
     return TRS_OK;
 }
 

@@ -3,8 +3,9 @@
 // The reference owns host Vec<f32> buffers (src/storage.rs:7-18); here a Storage is a block of
 // HBM handed out by a per-device size-bucketed cache so that the per-op fresh output allocation
 // the reference performs (from_owned_parts, src/tensor.rs:432-450) costs no cudaMalloc after
-// warm-up.  Freed blocks are reused in stream order on the library's streams; callers that mix
-// several streams on one device order them with events before freeing.
+// warm-up.  A freed block remembers the stream whose queued work may still use it: the same stream
+// gets it back at once (stream order protects it), another stream is first made to wait for that work,
+// and a request that names no stream only gets it once that stream has drained.
 #include <map>
 #include <mutex>
 #include <unordered_map>
@@ -19,9 +20,13 @@ std::atomic<int64_t> g_launches{0};
 
 namespace {
 constexpr int kMaxDevices = 16;
+struct FreeBlock {
+    void* ptr;
+    trs_stream last;       // stream whose queued work may still touch the block; NULL when nothing can
+};
 struct DeviceCache {
     std::mutex mu;
-    std::multimap<size_t, void*> free_blocks;          // rounded size -> block
+    std::multimap<size_t, FreeBlock> free_blocks;      // rounded size -> block
     std::unordered_map<void*, size_t> live;            // block -> rounded size
     int64_t in_use = 0, reserved = 0;
     int sms = 0;
@@ -36,7 +41,7 @@ size_t round_size(size_t bytes) {
 
 void release_all(DeviceCache& c) {
     for (auto& kv : c.free_blocks) {
-        cudaFree(kv.second);
+        cudaFree(kv.second.ptr);                          // cudaFree waits for the device to finish using the block
         c.reserved -= (int64_t)kv.first;
     }
     c.free_blocks.clear();
@@ -47,6 +52,9 @@ int32_t check_stream(trs_stream s) {
     if (!s) return fail(TRS_ERR_INVALID_ARGUMENT, "stream must not be NULL (use trs_stream_create)");
     return TRS_OK;
 }
+
+int32_t malloc_on_stream(trs_stream stream, size_t bytes, void** ptr) { return trs_malloc_async(stream->device, bytes, stream, ptr); }
+void free_on_stream(trs_stream stream, void* ptr) { trs_free_async(stream->device, ptr, stream); }
 
 int sm_count(int device) {
     DeviceCache& c = g_cache[device];
@@ -82,23 +90,37 @@ int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length) {
     return TRS_OK;
 }
 
-int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) {
+static int32_t cache_malloc(int32_t device, size_t bytes, trs_stream stream, void** ptr) {
     if (!ptr || device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad trs_malloc arguments");
+    if (stream && stream->device != device) return fail(TRS_ERR_INVALID_ARGUMENT, "stream belongs to device %d, not %d", stream->device, device);
     *ptr = nullptr;
     DeviceCache& c = g_cache[device];
     size_t rounded = round_size(bytes);
     std::lock_guard<std::mutex> lock(c.mu);
-    auto it = c.free_blocks.lower_bound(rounded);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     // Reuse only a block that wastes at most 1/8 of itself, so large blocks stay available for large requests.
-    if (it != c.free_blocks.end() && it->first <= rounded + rounded / 8) {
-        *ptr = it->second;
+    for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
+        FreeBlock& b = it->second;
+        if (b.last != nullptr && b.last != stream) {
+            if (stream) {
+                // order the new user behind everything the previous stream has queued (which includes its use of the block)
+                cudaEvent_t ev;
+                if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); continue; }
+                const bool ok = cudaEventRecord(ev, b.last->stream) == cudaSuccess && cudaStreamWaitEvent(stream->stream, ev, 0) == cudaSuccess;
+                cudaEventDestroy(ev);
+                if (!ok) { cudaGetLastError(); continue; }
+            } else if (cudaStreamQuery(b.last->stream) != cudaSuccess) {
+                cudaGetLastError();
+                continue;                                   // still busy: leave it for its own stream
+            }
+        }
+        *ptr = b.ptr;
         c.live[*ptr] = it->first;
         c.in_use += (int64_t)it->first;
         c.free_blocks.erase(it);
         return TRS_OK;
     }
-    DeviceGuard guard(device);
-    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, rounded);
     if (e == cudaErrorMemoryAllocation) {
@@ -117,7 +139,7 @@ int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) {
     return TRS_OK;
 }
 
-int32_t trs_free(int32_t device, void* ptr) {
+static int32_t cache_free(int32_t device, void* ptr, trs_stream stream) {
     if (!ptr) return TRS_OK;
     if (device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device");
     DeviceCache& c = g_cache[device];
@@ -125,9 +147,28 @@ int32_t trs_free(int32_t device, void* ptr) {
     auto it = c.live.find(ptr);
     if (it == c.live.end()) return fail(TRS_ERR_INVALID_ARGUMENT, "pointer was not allocated by trs_malloc on device %d", device);
     c.in_use -= (int64_t)it->second;
-    c.free_blocks.emplace(it->second, ptr);
+    c.free_blocks.emplace(it->second, FreeBlock{ptr, stream});
     c.live.erase(it);
     return TRS_OK;
+}
+
+// A stream that is going away can no longer be waited for: it has been drained, so its blocks are free for all.
+static void forget_stream(trs_stream stream) {
+    DeviceCache& c = g_cache[stream->device];
+    std::lock_guard<std::mutex> lock(c.mu);
+    for (auto& kv : c.free_blocks) if (kv.second.last == stream) kv.second.last = nullptr;
+}
+
+int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) { return cache_malloc(device, bytes, nullptr, ptr); }
+int32_t trs_free(int32_t device, void* ptr) { return cache_free(device, ptr, nullptr); }
+int32_t trs_malloc_async(int32_t device, size_t bytes, trs_stream stream, void** ptr) {
+    TRS_TRY(check_stream(stream));
+    return cache_malloc(device, bytes, stream, ptr);
+}
+int32_t trs_free_async(int32_t device, void* ptr, trs_stream stream) {
+    TRS_TRY(check_stream(stream));
+    if (stream->device != device) return fail(TRS_ERR_INVALID_ARGUMENT, "stream belongs to device %d, not %d", stream->device, device);
+    return cache_free(device, ptr, stream);
 }
 
 int32_t trs_empty_cache(int32_t device) {
@@ -175,6 +216,7 @@ int32_t trs_stream_destroy(trs_stream stream) {
     if (!stream) return TRS_OK;
     DeviceGuard guard(stream->device);
     cudaStreamSynchronize(stream->stream);
+    forget_stream(stream);
     cudaStreamDestroy(stream->stream);
     delete stream;
     return TRS_OK;
@@ -182,6 +224,7 @@ int32_t trs_stream_destroy(trs_stream stream) {
 
 int32_t trs_stream_sync(trs_stream stream) {
     TRS_TRY(check_stream(stream));
+    DeviceGuard guard(stream->device);
     TRS_CUDA(cudaStreamSynchronize(stream->stream));
     return gemm_check_status(stream->device);
 }

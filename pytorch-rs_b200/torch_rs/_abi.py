@@ -44,6 +44,11 @@ class GemmDesc(ctypes.Structure):
                 ("epilogue", ctypes.c_int32), ("algo", ctypes.c_int32)]
 
 
+class GemmPlanes(ctypes.Structure):
+    _fields_ = [("a_lo", ctypes.c_void_p), ("b_lo", ctypes.c_void_p), ("c_lo", ctypes.c_void_p),
+                ("a_flag", ctypes.c_void_p), ("b_flag", ctypes.c_void_p), ("c_flag", ctypes.c_void_p)]
+
+
 class TrsError(RuntimeError):
     def __init__(self, status, message):
         super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
@@ -59,6 +64,8 @@ _PROTOTYPES = {
     "trs_device_pci_bus_id": [ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32],
     "trs_malloc": [ctypes.c_int32, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)],
     "trs_free": [ctypes.c_int32, ctypes.c_void_p],
+    "trs_malloc_async": [ctypes.c_int32, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)],
+    "trs_free_async": [ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p],
     "trs_empty_cache": [ctypes.c_int32],
     "trs_memory_stats": [ctypes.c_int32, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)],
     "trs_malloc_host": [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)],
@@ -89,6 +96,19 @@ _PROTOTYPES = {
     "trs_colsum_f32_noalloc": [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p],
     "trs_matmul_f32": [ctypes.POINTER(GemmDesc), ctypes.c_void_p],
     "trs_matmul_select_algo": [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_int32)],
+    "trs_matmul_f32_planes": [ctypes.POINTER(GemmDesc), ctypes.POINTER(GemmPlanes), ctypes.c_void_p],
+    "trs_matmul_plan": [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32),
+                        ctypes.POINTER(ctypes.c_int32)],
+    "trs_split_lo_f32": [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p],
+    "trs_colsum_noalloc_geometry": [ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int32),
+                                    ctypes.POINTER(ctypes.c_int64)],
+    "trs_comm_unique_id": [ctypes.c_char_p],
+    "trs_comm_init_rank": [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)],
+    "trs_comm_allreduce_sum_f32": [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p],
+    "trs_comm_info": [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32),
+                      ctypes.POINTER(ctypes.c_int32)],
+    "trs_comm_destroy": [ctypes.c_void_p],
+    "trs_debug_wait_probe": [ctypes.c_void_p, ctypes.c_int64],
     "trs_jit_cache_size": [ctypes.POINTER(ctypes.c_int32)],
 }
 _SPECIAL = {

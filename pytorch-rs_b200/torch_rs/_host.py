@@ -29,6 +29,7 @@ _PROTOTYPES = {
     "trsh_device": [H, I32P],
     "trsh_flags": [H, I32P, I32P, I32P, I32P],
     "trsh_data_ptr": [H, HP],
+    "trsh_const_data_ptr": [H, HP],
     "trsh_shares_storage": [H, H, I32P],
     "trsh_permute": [H, ctypes.c_int32, I64P, HP],
     "trsh_transpose": [H, ctypes.c_int64, ctypes.c_int64, HP],
@@ -58,6 +59,14 @@ _PROTOTYPES = {
     "trsh_plan_scalar": [ctypes.c_int32, I64P, I64P, I64P],
     "trsh_plan_memory_format": [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, I64P, I64P, I32P, I64P],
     "trsh_plan_binary": [ctypes.c_int32, I64P, I64P, ctypes.c_int32, I64P, I64P, I32P, I64P, I64P],
+    "trsh_set_plane_cache": [ctypes.c_int32],
+    "trsh_has_operand_image": [H, I32P],
+    "trsh_comm_unique_id": [ctypes.c_char_p],
+    "trsh_comm_init": [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p],
+    "trsh_comm_destroy": [],
+    "trsh_comm_size": [I32P],
+    "trsh_all_reduce_grads": [HP, ctypes.c_int32],
+    "trsh_all_reduce": [H],
     "trsh_materialize": [H],
     "trsh_sync": [ctypes.c_int32],
     "trsh_stream": [ctypes.c_int32, HP],

@@ -3,9 +3,11 @@
 The reference has no distributed backend at all (every `torch.distributed.is_*_available()` is False,
 python/torch_rs/distributed/distributed_c10d.py:39-74); its only multi-process convention is the
 `LOCAL_RANK` environment variable (same file, 71-72), which is kept here.  The hot path shards by
-rows / batches with no exchange step; the single collective is the sum of the MLP weight gradients,
-issued as NCCL all-reduces (over NVLink / NVSwitch) that are stream-ordered after the kernels that
-produce the gradients.  PyTorch is used for the process group only; it never computes a result.
+rows / batches with no exchange step; the single collective is the sum of the MLP weight gradients:
+NCCL all-reduces (over NVLink / NVSwitch) issued by the engine itself through the C ABI
+(`trs_comm_*`) on a side stream, each one behind the kernel that produced that gradient, so the
+exchange overlaps the rest of the backward pass.  `torch.distributed` (gloo) is the control plane
+only: rendezvous, barriers, handing the communicator id to the ranks, small host-side reductions.
 """
 from __future__ import annotations
 
@@ -39,28 +41,40 @@ def get_world_size() -> int:
 
 
 def init_process_group(backend: str | None = None) -> str:
-    """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.  `nccl` when this
-    rank has a CUDA device, else `gloo` (used by the CPU tests of the host-side logic)."""
-    import torch as pt
+    """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.  `nccl` (the default
+    when this rank has a CUDA device) adds the engine's NCCL communicator on device LOCAL_RANK for the
+    data path; `gloo` is the control plane alone (used by the CPU tests of the host-side logic)."""
     import torch.distributed as dist
     if _state["initialized"]:
         return _state["backend"]
     if backend is None:
         backend = "nccl" if _device.device_count() > 0 else "gloo"
-    kwargs = {}
-    if backend == "nccl":
-        local = get_node_local_rank(0)
-        pt.cuda.set_device(local)
-        kwargs["device_id"] = pt.device("cuda", local)
-    dist.init_process_group(backend, **kwargs)
+    if backend not in ("nccl", "gloo"):
+        raise ValueError(f"unknown backend {backend!r}")
+    if not dist.is_initialized():
+        dist.init_process_group("gloo")
     _state.update(initialized=True, backend=backend)
+    if backend == "nccl" and get_world_size() > 1:
+        import ctypes
+        from . import _host
+        ident = ctypes.create_string_buffer(128)
+        if get_rank() == 0:
+            _host.check(_host.lib().trsh_comm_unique_id(ident))
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=0)
+        _host.check(_host.lib().trsh_comm_init(get_node_local_rank(0), get_world_size(), get_rank(), box[0]))
     return backend
 
 
 def destroy_process_group() -> None:
     import torch.distributed as dist
     if _state["initialized"]:
-        dist.destroy_process_group()
+        if _state["backend"] == "nccl":
+            from . import _host
+            _host.check(_host.lib().trsh_comm_destroy())
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
         _state.update(initialized=False, backend=None)
 
 
@@ -92,9 +106,13 @@ def bind_to_device_numa_node(device_index: int) -> int | None:
     bus = buf.value.decode().lower()
     try:
         node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
-        if node < 0:
-            return None
-        cpus = _parse_cpu_list(open(f"/sys/devices/system/node/node{node}/cpulist").read())
+        if node >= 0:
+            cpus = _parse_cpu_list(open(f"/sys/devices/system/node/node{node}/cpulist").read())
+        else:
+            # no NUMA information for the device (a virtualised host): the CPUs local to its PCIe root, if listed
+            cpus = _parse_cpu_list(open(f"/sys/bus/pci/devices/{bus}/local_cpulist").read())
+            if len(cpus) >= len(os.sched_getaffinity(0)):
+                return None                      # "local" is every CPU: nothing to bind to
         allowed = cpus & os.sched_getaffinity(0)
         if not allowed:
             return None
@@ -114,41 +132,15 @@ def shard_bounds(total: int, rank: int, world: int) -> tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
-class _DeviceSpan:
-    """Exposes `count` float32 at a raw device address through __cuda_array_interface__ (zero copy)."""
-
-    def __init__(self, ptr: int, count: int):
-        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
-
-
 def all_reduce_(tensor) -> None:
-    """In-place sum of a contiguous CUDA tensor over all ranks.  Enqueued behind the engine's stream
-    (the collective waits for the kernels that wrote `tensor`; later engine work waits for it)."""
-    import torch as pt
-    import torch.distributed as dist
+    """In-place sum of a contiguous CUDA tensor over all ranks, on the engine's exchange stream: it
+    waits for the kernels that wrote `tensor`, and later engine work waits for it."""
+    from . import _host
     if not _state["initialized"] or get_world_size() == 1:
         return
     if not tensor.is_contiguous():
         raise RuntimeError("all_reduce_ needs a contiguous tensor")
-    index = tensor.device.index
-    ptr = tensor.data_ptr()          # forces the value onto the device
-    view = pt.as_tensor(_DeviceSpan(ptr, tensor.numel()), device=f"cuda:{index}")
-    stream = _state["streams"].get(index)
-    if stream is None:
-        raw = _engine_cuda_stream(index)
-        stream = _state["streams"][index] = pt.cuda.ExternalStream(raw, device=f"cuda:{index}")
-    with pt.cuda.stream(stream):
-        dist.all_reduce(view, op=dist.ReduceOp.SUM)
-
-
-def _engine_cuda_stream(index: int) -> int:
-    import ctypes
-    from . import _abi, _host
-    handle = ctypes.c_void_p()
-    _host.check(_host.lib().trsh_stream(index, ctypes.byref(handle)))
-    raw = ctypes.c_void_p()
-    _abi.check(_abi.lib().trs_stream_handle(handle, ctypes.byref(raw)))
-    return raw.value or 0
+    _host.check(_host.lib().trsh_all_reduce(tensor._h))
 
 
 def all_reduce_host(array: np.ndarray, op: str = "sum") -> np.ndarray:
@@ -157,16 +149,19 @@ def all_reduce_host(array: np.ndarray, op: str = "sum") -> np.ndarray:
     import torch.distributed as dist
     if not _state["initialized"] or get_world_size() == 1:
         return array
-    t = pt.from_numpy(np.ascontiguousarray(array))
-    if _state["backend"] == "nccl":
-        t = t.cuda()
+    t = pt.from_numpy(np.ascontiguousarray(array).copy())
     dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.MAX)
-    return t.cpu().numpy()
+    return t.numpy()
 
 
 def all_reduce_gradients(parameters) -> None:
-    """Sum `.grad` of every parameter over the ranks (data-parallel MLP step)."""
-    for p in parameters:
-        g = p.grad
-        if g is not None:
-            all_reduce_(g)
+    """Sum `.grad` of every parameter over the ranks (data-parallel MLP step).  Each gradient's
+    all-reduce starts on the exchange stream as soon as the kernel that produced it has finished, in
+    the order given; the engine's compute stream resumes after the last one."""
+    import ctypes
+    from . import _host
+    if not _state["initialized"] or get_world_size() == 1:
+        return
+    params = [p for p in parameters]
+    handles = (ctypes.c_void_p * len(params))(*[p._h for p in params])
+    _host.check(_host.lib().trsh_all_reduce_grads(handles, len(params)))

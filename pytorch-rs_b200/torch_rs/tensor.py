@@ -195,6 +195,13 @@ class Tensor:
         _host.check(_host.lib().trsh_data_ptr(self._h, ctypes.byref(p)))
         return p.value or 0
 
+    def _const_data_ptr(self):
+        """Device address for read-only use (checks, descriptors); unlike `data_ptr()` it does not make the
+        engine treat the storage as writable from outside."""
+        p = ctypes.c_void_p()
+        _host.check(_host.lib().trsh_const_data_ptr(self._h, ctypes.byref(p)))
+        return p.value or 0
+
     def shares_storage_with(self, other):
         r = ctypes.c_int32()
         _host.check(_host.lib().trsh_shares_storage(self._h, other._h, ctypes.byref(r)))
