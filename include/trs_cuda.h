@@ -79,7 +79,7 @@ typedef enum trs_op {
     TRS_OP_DIV = 4,        /* a / b      src/tensor.rs:2245 */
     TRS_OP_NEG = 5,        /* sign flip  src/tensor.rs:4388 */
     TRS_OP_RELU = 6,       /* src/tensor.rs:4392-4400: +-0 pass through, NaN -> +0 */
-    TRS_OP_EXP = 7,        /* src/tensor.rs:2398 (libm expf; here within 2 ulp of it) */
+    TRS_OP_EXP = 7,        /* src/tensor.rs:2398 (libm expf; here within 1 ulp of glibc's) */
     TRS_OP_RELU_VJP = 8,   /* a = saved input, b = upstream   src/tensor.rs:4422-4432 */
     TRS_OP_RECIP = 9,      /* 1.0 * (1.0 / a)   src/tensor.rs:2348-2355 */
     TRS_OP_SQRT = 10,      /* src/tensor.rs:4402-4414 */

@@ -286,6 +286,28 @@ __device__ __forceinline__ float trs_sqrt(float v) {
     u32 b = __float_as_uint(v), mag = b & 0x7fffffffu;
     return ((b >> 31) != 0u && mag != 0u && mag <= 0x7f800000u) ? __uint_as_float(0x7fc00000u) : __fsqrt_rn(v);
 }
+// exp within 1 ulp of a correctly rounded expf (the reference calls the platform's libm expf, src/tensor.rs:2398-2400;
+// glibc's is within 0.502 ulp of the true value, CUDA's expf only within 2).  Cody-Waite reduction x = j ln2 + r with
+// ln2 in two parts, |r| <= ln2/2, exp(r) = 1 + r + r^2 q(r) with a degree-4 minimax q (error 3e-9), result scaled by
+// 2^j in two exact-or-once-rounded steps so that subnormal results round once.  Checked against glibc expf on every
+// float32 in [-104.5, 89.5]: never more than 1 ulp apart, 99.2 % of the inputs bit-equal.  exp(+-0) = exp(+-denormal)
+// = 1, exp(x > 88.73) = +inf, exp(x < -103.98) = +0, NaN stays NaN (the clamp's comparisons are false for it).
+__device__ __forceinline__ float trs_exp(float x) {
+    const float t = x < -110.0f ? -110.0f : (x > 90.0f ? 90.0f : x);
+    const float j = __fsub_rn(__fmaf_rn(t, 1.44269502f, 12582912.0f), 12582912.0f);    // nearest integer to t / ln2
+    float r = __fmaf_rn(j, -0.693145752f, t);
+    r = __fmaf_rn(j, -1.42860677e-06f, r);
+    float q = __uint_as_float(0x3ab6da3fu);               // 0x1.6db47ep-10
+    q = __fmaf_rn(q, r, __uint_as_float(0x3c091dc9u));    // 0x1.123b92p-7
+    q = __fmaf_rn(q, r, __uint_as_float(0x3d2aaa2fu));    // 0x1.55545ep-5
+    q = __fmaf_rn(q, r, __uint_as_float(0x3e2aaa47u));    // 0x1.55548ep-3
+    q = __fmaf_rn(q, r, 0.5f);
+    const float p = __fadd_rn(__fmaf_rn(q, __fmul_rn(r, r), r), 1.0f);
+    const int ji = __float2int_rn(j);                     // 0 for NaN
+    const int h = ji >> 1;
+    const float s1 = __uint_as_float((u32)(h + 127) << 23), s2 = __uint_as_float((u32)(ji - h + 127) << 23);
+    return __fmul_rn(__fmul_rn(p, s1), s2);
+}
 __device__ __forceinline__ u32 trs_div(u32 n, u32 magic, u32 shift) { return (__umulhi(n, magic) + n) >> shift; }
 )SRC";
 
@@ -313,7 +335,7 @@ void emit_chain(std::ostringstream& s, const trs_program* prog) {
             case TRS_OP_DIV: s << d << "__fdiv_rn(" << a << ", " << b << ");\n"; break;
             case TRS_OP_NEG: s << d << "trs_neg(" << a << ");\n"; break;
             case TRS_OP_RELU: s << d << "trs_relu(" << a << ");\n"; break;
-            case TRS_OP_EXP: s << d << "expf(" << a << ");\n"; break;
+            case TRS_OP_EXP: s << d << "trs_exp(" << a << ");\n"; break;
             case TRS_OP_RELU_VJP: s << d << "trs_relu_vjp(" << a << ", " << b << ");\n"; break;
             case TRS_OP_RECIP: s << d << "__fmul_rn(1.0f, __frcp_rn(" << a << "));\n"; break;
             case TRS_OP_SQRT: s << d << "trs_sqrt(" << a << ");\n"; break;

@@ -163,6 +163,15 @@ def get_float32_matmul_precision() -> str:
     return "highest"
 
 
+def set_operand_image_cache(enabled: bool) -> None:
+    """Tensor-core matmul operands are split into a TF32 `hi` part (read in place) and a `lo` image.  With the
+    cache on (the default) the image of a storage is computed once, kept beside it and reused by every matmul
+    that reads the storage -- a storage's values never change (src/storage.rs:7-18) -- and a matmul whose result
+    feeds another matmul writes that result's image in its epilogue.  Off: every matmul prepares its operands
+    itself.  Results are bit-identical either way."""
+    _host.check(_host.lib().trsh_set_plane_cache(1 if enabled else 0))
+
+
 def is_grad_enabled() -> bool:
     on = ctypes.c_int32()
     _host.check(_host.lib().trsh_is_grad_enabled(ctypes.byref(on)))

@@ -202,6 +202,12 @@ class Tensor:
         _host.check(_host.lib().trsh_const_data_ptr(self._h, ctypes.byref(p)))
         return p.value or 0
 
+    def _has_operand_image(self):
+        """Whether this tensor's storage carries a cached matmul operand image (see set_operand_image_cache)."""
+        r = ctypes.c_int32()
+        _host.check(_host.lib().trsh_has_operand_image(self._h, ctypes.byref(r)))
+        return bool(r.value)
+
     def shares_storage_with(self, other):
         r = ctypes.c_int32()
         _host.check(_host.lib().trsh_shares_storage(self._h, other._h, ctypes.byref(r)))

@@ -24,10 +24,22 @@ def cpu_main(out_path):
     partial = np.array([vec[begin:end].sum()])
     summed = dist.all_reduce_host(partial)
     biggest = dist.all_reduce_host(np.array([float(rank)]), op="max")
+    # the collective's C entry points refuse bad arguments on the host, before any NCCL or CUDA call
+    import ctypes
+    from torch_rs import _abi, _host
+    lib = _abi.lib()
+    comm = ctypes.c_void_p()
+    refused = [lib.trs_comm_init_rank(0, world, world, b"\0" * 128, ctypes.byref(comm)),     # rank outside the job
+               lib.trs_comm_init_rank(-1, world, rank, b"\0" * 128, ctypes.byref(comm)),     # no such device
+               lib.trs_comm_allreduce_sum_f32(None, None, 16, None)]                          # no communicator
+    size = ctypes.c_int32(-1)
+    _host.check(_host.lib().trsh_comm_size(ctypes.byref(size)))                               # gloo only: no engine communicator
+    dist.all_reduce_gradients([])                                                             # nothing to do, must not raise
+    all_refused = dist.all_reduce_host(np.array([float(all(r == 1 for r in refused) and size.value == 1)]), op="sum")
     dist.barrier()
     if rank == 0:
         json.dump({"backend": backend, "world": world, "covered": int(covered[0]), "total": total,
-                   "sum": float(summed[0]), "expected_sum": float(vec.sum()), "max_rank": float(biggest[0]),
+                   "sum": float(summed[0]), "expected_sum": float(vec.sum()), "max_rank": float(biggest[0]), "ranks_refusing_bad_arguments": float(all_refused[0]),
                    "local_rank": dist.get_node_local_rank()}, open(out_path, "w"))
     dist.destroy_process_group()
 

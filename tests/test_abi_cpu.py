@@ -106,3 +106,69 @@ def test_huge_contiguous_extent_is_split_for_32_bit_indexing():
     out = fake_operand(0x800000000, [n], [1])
     status, klass = prepare([("relu", 0, 0, 0)], [1], [x], [out])
     assert status == 0 and klass == "vector", _abi.lib().trs_last_error_message()
+
+
+def test_allocation_free_column_sum_never_plans_more_partials_than_its_array_holds():
+    """The fixed 1 MiB array bounds chunks * cols.  A 148-SM GPU never asks for more, so the bound is exercised with
+    a larger made-up SM count (no device needed: this is host arithmetic)."""
+    lib = _abi.lib()
+    limit = 262144
+    chunks, per = ctypes.c_int32(), ctypes.c_int64()
+    for sms, rows, cols in [(148, 65536, 4096), (1024, 1 << 20, 4096), (4096, 1 << 22, 100000), (1024, 1 << 20, limit),
+                            (1024, 3, 7), (148, 1, 1)]:
+        assert lib.trs_colsum_noalloc_geometry(sms, rows, cols, ctypes.byref(chunks), ctypes.byref(per)) == 0
+        assert 1 <= chunks.value and chunks.value * cols <= limit
+        assert (chunks.value - 1) * per.value < rows <= chunks.value * per.value      # the chunks cover every row once
+    assert lib.trs_colsum_noalloc_geometry(1024, 1 << 20, 4096, ctypes.byref(chunks), ctypes.byref(per)) == 0
+    assert chunks.value == limit // 4096                                                 # the bound is what decided here
+    assert lib.trs_colsum_noalloc_geometry(148, 8, limit + 1, ctypes.byref(chunks), ctypes.byref(per)) == 1
+
+
+def gemm_desc(m, n, k, a_strides, b_strides, batch=1, algo="auto", a=0x10000000, b=0x30000000):
+    d = _abi.GemmDesc()
+    d.batch, d.m, d.n, d.k = batch, m, n, k
+    d.a, d.b, d.c = a, b, 0x50000000
+    d.a_batch_stride, d.a_row_stride, d.a_col_stride = m * k, a_strides[0], a_strides[1]
+    d.b_batch_stride, d.b_row_stride, d.b_col_stride = k * n, b_strides[0], b_strides[1]
+    d.c_batch_stride, d.c_row_stride = m * n, n
+    d.algo = _abi.GEMM_ALGOS[algo]
+    return d
+
+
+def test_matmul_plan_tells_which_operand_images_would_be_read():
+    lib = _abi.lib()
+
+    def plan(d):
+        algo, a, b = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+        assert lib.trs_matmul_plan(ctypes.byref(d), ctypes.byref(algo), ctypes.byref(a), ctypes.byref(b)) == 0
+        return algo.value, a.value, b.value
+
+    # plain A @ B, 4096^3: the pair kernel reads A K-major and B MN-major, both in place
+    assert plan(gemm_desc(4096, 4096, 4096, (4096, 1), (4096, 1))) == (3, 1, 1)
+    # X[65536, 4096] @ W1: each element of W1 is reused 65,536 times, so it is re-laid K-major once per call
+    assert plan(gemm_desc(65536, 4096, 4096, (4096, 1), (4096, 1))) == (3, 1, 0)
+    # X^T @ dZ (weight gradient): both operands row-contiguous, read MN-major in place
+    assert plan(gemm_desc(4096, 4096, 65536, (1, 4096), (4096, 1))) == (3, 1, 1)
+    # W.mT per batch (config 4): K-major on both sides
+    assert plan(gemm_desc(1024, 1024, 1024, (1024, 1), (1, 1024), batch=64)) == (3, 1, 1)
+    # unaligned base: the operand is re-laid, an image of it would not be read
+    assert plan(gemm_desc(512, 512, 512, (512, 1), (1, 512), a=0x10000004)) == (3, 0, 1)
+    # tiny product: the FP32 kernel, no images
+    assert plan(gemm_desc(8, 8, 8, (8, 1), (8, 1))) == (1, 0, 0)
+
+
+def test_collective_and_stream_ordered_entry_points_check_their_arguments():
+    lib = _abi.lib()
+    assert lib.trs_comm_allreduce_sum_f32(None, None, 0, None) == 1
+    assert b"comm is NULL" in lib.trs_last_error_message()
+    comm = ctypes.c_void_p()
+    assert lib.trs_comm_init_rank(0, 2, 2, b"\0" * 128, ctypes.byref(comm)) == 1
+    assert b"outside a job of 2 ranks" in lib.trs_last_error_message()
+    assert lib.trs_comm_init_rank(0, 2, 0, None, ctypes.byref(comm)) == 1
+    assert lib.trs_comm_destroy(None) == 0
+    assert lib.trs_comm_info(None, None, None, None) == 1
+    p = ctypes.c_void_p()
+    assert lib.trs_malloc_async(0, 1024, None, ctypes.byref(p)) == 1           # a stream is required
+    assert lib.trs_free_async(0, None, None) == 1
+    assert lib.trs_debug_wait_probe(None, 1000) == 1
+    assert lib.trs_split_lo_f32(None, 4, None, None, None) == 1

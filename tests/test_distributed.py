@@ -56,6 +56,7 @@ def test_world_size_two_gloo_sharding_and_collectives(tmp_path):
     assert r["covered"] == r["total"]
     assert r["sum"] == r["expected_sum"]
     assert r["max_rank"] == 1.0 and r["local_rank"] == 0
+    assert r["ranks_refusing_bad_arguments"] == 2.0
 
 
 @pytest.mark.gpu
