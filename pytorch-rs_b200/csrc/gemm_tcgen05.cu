@@ -182,8 +182,11 @@ struct EpilogueArgs {
     long long c_batch_stride, c_row_stride;
     int m, n, k_blocks, epilogue;
     int tiles_m, tiles_n, total_tiles;
-    int whole_tiles;      // work items [0, whole_tiles) are complete tiles; each later tile is two half-K items added atomically
+    int whole_tiles;      // work items [0, whole_tiles) are complete tiles; each later tile is cut into `parts` items along K
     int total_items;
+    int parts;            // K parts per tile of the last, partly filled round (1 = no cut)
+    float* partials;      // [cut tile][part][tile rows][BN] partial sums of the cut tiles
+    unsigned int* arrivals;  // [cut tile][row slab] zeroed counters: the last part to arrive adds the parts up and stores C
     int a_mn, b_mn;       // pair kernel: the operand's tiles are MN-major (unit stride along its rows) instead of K-major
     float* c_lo;          // optional: lo image of C (tf32(c - trunc_tf32(c))), laid out like C, for the matmul that reads C next
     unsigned int* c_flag; // with c_lo: set to 1 when an inf / NaN is stored
@@ -206,26 +209,86 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
     tile_m = first_m + (in_band - tile_n * band_rows);
 }
 
-// Work item -> tile and K-block range.  When the last round of tiles would leave more than half of
-// the SMs idle, those tiles are cut in two along K; both halves add into a zeroed C (two commutative
-// additions onto zero, so the result does not depend on which half lands first).
-__device__ __forceinline__ void decode_item(int w, const EpilogueArgs& e, int& tile, int& kb_begin, int& kb_end, bool& split) {
-    if (w < e.whole_tiles) { tile = w; kb_begin = 0; kb_end = e.k_blocks; split = false; return; }
+// Work item -> tile and K-block range.  When the last round of tiles would leave SMs idle, its tiles are cut
+// into `parts` items along K that run side by side.  Every item of a cut tile writes its partial sums to scratch;
+// whichever arrives last adds the parts up in part order (so the result does not depend on who finishes when),
+// applies the epilogue and stores C.  Nobody waits for anybody.
+__device__ __forceinline__ void decode_item(int w, const EpilogueArgs& e, int& tile, int& kb_begin, int& kb_end, int& part) {
+    if (w < e.whole_tiles) { tile = w; kb_begin = 0; kb_end = e.k_blocks; part = -1; return; }
     const int r = w - e.whole_tiles;
-    tile = e.whole_tiles + (r >> 1);
-    const int mid = e.k_blocks >> 1;
-    kb_begin = (r & 1) ? mid : 0;
-    kb_end = (r & 1) ? e.k_blocks : mid;
-    split = true;
+    const int cut = r / e.parts;
+    part = r - cut * e.parts;
+    tile = e.whole_tiles + cut;
+    kb_begin = (int)(((long long)e.k_blocks * part) / e.parts);
+    kb_end = (int)(((long long)e.k_blocks * (part + 1)) / e.parts);
+}
+
+// Fused epilogue and store of 32 consecutive columns of one output row.
+__device__ __forceinline__ void finish_chunk(const EpilogueArgs& e, float (&v)[32], long long idx0, long long col0, bool vec_ok) {
+    const bool full_cols = col0 + 32 <= e.n;
+    if (e.epilogue == TRS_EPI_BIAS || e.epilogue == TRS_EPI_BIAS_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (full_cols || col0 + j < e.n) v[j] = __fadd_rn(v[j], __ldg(e.bias + col0 + j));
+    }
+    if (e.epilogue == TRS_EPI_BIAS_RELU && e.preact) {
+        if (full_cols && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.preact + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.preact[idx0 + j] = v[j];
+        }
+    }
+    if (e.epilogue == TRS_EPI_BIAS_RELU || e.epilogue == TRS_EPI_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = ref_relu(v[j]);
+    }
+    if (e.epilogue == TRS_EPI_RELU_VJP) {
+        if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.aux) & 15u) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 z = __ldcs(reinterpret_cast<const float4*>(e.aux + idx0 + j));
+                v[j] = ref_relu_vjp(z.x, v[j]); v[j + 1] = ref_relu_vjp(z.y, v[j + 1]);
+                v[j + 2] = ref_relu_vjp(z.z, v[j + 2]); v[j + 3] = ref_relu_vjp(z.w, v[j + 3]);
+            }
+        } else {
+            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
+        }
+    }
+    if (e.c_lo) {
+        // lo image of the stored values, for the matmul that consumes C as an operand
+        float l[32];
+        bool nonfinite = false;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) nonfinite |= lo_of(v[j], l[j]);
+        if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.c_lo) & 15u) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c_lo + idx0 + j) = make_float4(l[j], l[j + 1], l[j + 2], l[j + 3]);
+        } else {
+            nonfinite = false;
+            for (int j = 0; j < 32; ++j) if (col0 + j < e.n) { e.c_lo[idx0 + j] = l[j]; nonfinite |= (__float_as_uint(v[j]) & 0x7f800000u) == 0x7f800000u; }
+        }
+        if (nonfinite) *reinterpret_cast<volatile unsigned int*>(e.c_flag) = 1u;
+    }
+    if (full_cols && vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+        for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.c[idx0 + j] = v[j];
+    }
 }
 
 // Epilogue of one warp for one tile: reads its 32 accumulator rows (TMEM lanes) 32 columns at a time,
 // hands the accumulator back as soon as the last columns are in registers, applies the fused
 // epilogue and stores.  `tmem_acc` addresses the warp's lanes at the accumulator's first column;
 // `empty_bar_addr` is the accumulator-empty barrier (a cluster address of the leader's barrier when kPair).
+// For an item of a cut tile (`part` >= 0) the columns go to the partial-sum scratch instead; `slab` is this
+// warp's 32-row slab of the tile (0 .. tile rows / 32 - 1) and `cut` the tile's index among the cut tiles.
 template <bool kPair>
 __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_t tmem_acc, long long row, long long batch_off, int tile_n,
-                                                  bool split, bool vec_ok, int lane, uint32_t empty_bar_addr) {
+                                                  int part, int cut, int slab, bool vec_ok, int lane, uint32_t empty_bar_addr) {
+    constexpr int kTileRows = kPair ? 2 * BM : BM;
+    float* my_partial = nullptr;
+    if (part >= 0) my_partial = e.partials + (((long long)cut * e.parts + part) * kTileRows + slab * 32 + lane) * BN;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -246,65 +309,47 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_
             if (lane == 0) { if (kPair) mbar_arrive_cluster(empty_bar_addr); else mbar_arrive(empty_bar_addr); }
         }
         const long long col0 = (long long)tile_n * BN + c0;
+        if (part >= 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(my_partial + c0 + j), make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+            continue;
+        }
         if (row < e.m && col0 < e.n) {
-            const long long idx0 = batch_off + row * e.c_row_stride + col0;
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            const bool full_cols = col0 + 32 <= e.n;
-            if (e.epilogue == TRS_EPI_BIAS || e.epilogue == TRS_EPI_BIAS_RELU) {
+            finish_chunk(e, v, batch_off + row * e.c_row_stride + col0, col0, vec_ok);
+        }
+    }
+    if (part < 0) return;
+    // This slab's part is in scratch.  Count it; the last of the tile's parts to get here finishes the slab.
+    __threadfence();
+    __syncwarp();
+    unsigned int earlier = 0;
+    if (lane == 0) earlier = atomicAdd(e.arrivals + (long long)cut * (kTileRows / 32) + slab, 1u);
+    earlier = __shfl_sync(0xffffffffu, earlier, 0);
+    if (earlier != (unsigned int)(e.parts - 1)) return;
+    __threadfence();
+    const float* first = e.partials + (((long long)cut * e.parts) * kTileRows + slab * 32 + lane) * BN;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        const long long col0 = (long long)tile_n * BN + c0;
+        if (!(row < e.m && col0 < e.n)) continue;
+        float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) if (full_cols || col0 + j < e.n) v[j] = __fadd_rn(v[j], __ldg(e.bias + col0 + j));
-            }
-            if (e.epilogue == TRS_EPI_BIAS_RELU && e.preact) {
-                if (full_cols && vec_ok) {
+        for (int j = 0; j < 32; j += 4) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(first + c0 + j));
+            v[j] = t.x; v[j + 1] = t.y; v[j + 2] = t.z; v[j + 3] = t.w;
+        }
+        for (int q = 1; q < e.parts; ++q) {                 // fixed order: part 0 + part 1 + ...
+            const float* next = first + (long long)q * kTileRows * BN;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.preact + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                } else {
-                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.preact[idx0 + j] = v[j];
-                }
-            }
-            if (e.epilogue == TRS_EPI_BIAS_RELU || e.epilogue == TRS_EPI_RELU) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = ref_relu(v[j]);
-            }
-            if (e.epilogue == TRS_EPI_RELU_VJP) {
-                if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.aux) & 15u) == 0)) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 z = __ldcs(reinterpret_cast<const float4*>(e.aux + idx0 + j));
-                        v[j] = ref_relu_vjp(z.x, v[j]); v[j + 1] = ref_relu_vjp(z.y, v[j + 1]);
-                        v[j + 2] = ref_relu_vjp(z.z, v[j + 2]); v[j + 3] = ref_relu_vjp(z.w, v[j + 3]);
-                    }
-                } else {
-                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) v[j] = ref_relu_vjp(e.aux[idx0 + j], v[j]);
-                }
-            }
-            if (e.c_lo && !split) {
-                // lo image of the stored values, for the matmul that consumes C as an operand
-                float l[32];
-                bool nonfinite = false;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) nonfinite |= lo_of(v[j], l[j]);
-                if (full_cols && vec_ok && ((reinterpret_cast<uintptr_t>(e.c_lo) & 15u) == 0)) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c_lo + idx0 + j) = make_float4(l[j], l[j + 1], l[j + 2], l[j + 3]);
-                } else {
-                    nonfinite = false;
-                    for (int j = 0; j < 32; ++j) if (col0 + j < e.n) { e.c_lo[idx0 + j] = l[j]; nonfinite |= (__float_as_uint(v[j]) & 0x7f800000u) == 0x7f800000u; }
-                }
-                if (nonfinite) *reinterpret_cast<volatile unsigned int*>(e.c_flag) = 1u;
-            }
-            if (split) {
-                // half-K partial (plain product only): add onto the zeroed output
-                for (int j = 0; j < 32; ++j) if (col0 + j < e.n) atomicAdd(e.c + idx0 + j, v[j]);
-            } else if (full_cols && vec_ok) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(e.c + idx0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-                for (int j = 0; j < 32; ++j) if (col0 + j < e.n) e.c[idx0 + j] = v[j];
+            for (int j = 0; j < 32; j += 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(next + c0 + j));
+                v[j] = __fadd_rn(v[j], t.x); v[j + 1] = __fadd_rn(v[j + 1], t.y); v[j + 2] = __fadd_rn(v[j + 2], t.z); v[j + 3] = __fadd_rn(v[j + 3], t.w);
             }
         }
+        finish_chunk(e, v, batch_off + row * e.c_row_stride + col0, col0, vec_ok);
     }
 }
 
@@ -348,8 +393,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             uint32_t g = 0;                                           // stage uses so far, over all tiles
             for (int w = blockIdx.x; w < e.total_items && !failed; w += gridDim.x) {
                 int t, kb_begin, kb_end, batch, tile_m, tile_n;
-                bool split;
-                decode_item(w, e, t, kb_begin, kb_end, split);
+                int part;
+                decode_item(w, e, t, kb_begin, kb_end, part);
                 decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % STAGES, round = g / STAGES;
@@ -372,8 +417,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             uint32_t g = 0, it = 0;
             for (int w = blockIdx.x; w < e.total_items && !failed; w += gridDim.x, ++it) {
                 int t, kb_begin, kb_end;
-                bool split;
-                decode_item(w, e, t, kb_begin, kb_end, split);
+                int part;
+                decode_item(w, e, t, kb_begin, kb_end, part);
                 const uint32_t acc = it & 1, use = it >> 1;
                 // the epilogue must have drained this accumulator's previous tile
                 if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, e.wait_cycles)) { failed = true; break; }
@@ -409,8 +454,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         bool failed = false;
         for (int w = blockIdx.x; w < e.total_items && !failed; w += gridDim.x, ++it) {
             int t, kb_begin, kb_end, batch, tile_m, tile_n;
-            bool split;
-            decode_item(w, e, t, kb_begin, kb_end, split);
+            int part;
+            decode_item(w, e, t, kb_begin, kb_end, part);
             decode_tile(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
             const uint32_t acc = it & 1, use = it >> 1;
             if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1, e.wait_cycles)) {
@@ -421,8 +466,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long row = (long long)tile_m * BM + quarter * 32 + lane;
             const long long batch_off = (long long)batch * e.c_batch_stride;
-            drain_accumulator<false>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, split, vec_ok, lane,
-                                     smem_u32(&acc_empty[acc]));
+            drain_accumulator<false>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, part,
+                                     (t - e.whole_tiles), quarter, vec_ok, lane, smem_u32(&acc_empty[acc]));
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -499,8 +544,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             uint32_t g = 0;
             for (int w = pair; w < e.total_items && !failed; w += pairs) {
                 int t, kb_begin, kb_end, batch, tile_m, tile_n;
-                bool split;
-                decode_item(w, e, t, kb_begin, kb_end, split);
+                int part;
+                decode_item(w, e, t, kb_begin, kb_end, part);
                 decode_tile<PAIR_GROUP_M>(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
                 const int a_row = tile_m * (2 * BM) + (int)rank * BM;
                 const int b_row = tile_n * BN + (int)rank * (BN / 2);
@@ -540,8 +585,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             const uint32_t idesc = kInstrDescPair | (e.a_mn ? (1u << 15) : 0u) | (e.b_mn ? (1u << 16) : 0u);
             for (int w = pair; w < e.total_items && !failed; w += pairs, ++it) {
                 int t, kb_begin, kb_end;
-                bool split;
-                decode_item(w, e, t, kb_begin, kb_end, split);
+                int part;
+                decode_item(w, e, t, kb_begin, kb_end, part);
                 const uint32_t acc = it & 1, use = it >> 1;
                 if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, e.wait_cycles)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -583,8 +628,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
         uint32_t it = 0;
         for (int w = pair; w < e.total_items; w += pairs, ++it) {
             int t, kb_begin, kb_end, batch, tile_m, tile_n;
-            bool split;
-            decode_item(w, e, t, kb_begin, kb_end, split);
+            int part;
+            decode_item(w, e, t, kb_begin, kb_end, part);
             decode_tile<PAIR_GROUP_M>(t, e.tiles_m, e.tiles_n, batch, tile_m, tile_n);
             const uint32_t acc = it & 1, use = it >> 1;
             if (!mbar_wait(smem_u32(&acc_full[acc]), use & 1, e.wait_cycles)) {
@@ -594,8 +639,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gr
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long row = (long long)tile_m * (2 * BM) + (long long)rank * BM + quarter * 32 + lane;
             const long long batch_off = (long long)batch * e.c_batch_stride;
-            drain_accumulator<true>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, split, vec_ok, lane,
-                                    map_to_cta(smem_u32(&acc_empty[acc]), 0));
+            drain_accumulator<true>(e, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, row, batch_off, tile_n, part,
+                                    (t - e.whole_tiles), (int)rank * 4 + quarter, vec_ok, lane, map_to_cta(smem_u32(&acc_empty[acc]), 0));
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -994,6 +1039,14 @@ int32_t gemm_split_lo(const float* src, long long count, float* lo, unsigned int
     return TRS_OK;
 }
 
+namespace {
+struct ScratchGuard {       // handed back when the call returns: reuse is ordered behind this stream's work
+    trs_stream s;
+    void* p;
+    ~ScratchGuard() { if (p) free_on_stream(s, p); }
+};
+}  // namespace
+
 // Split (where no image was given) + GEMM + the gated exact-FP32 recompute.
 int32_t gemm_tc_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, trs_stream stream) {
     if (g.m > INT32_MAX || g.n > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "matrix extent above 2^31");
@@ -1024,10 +1077,7 @@ int32_t gemm_tc_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, tr
     const long long b_floats = rb.given ? 0 : (rb.mn ? g.batch * g.k * g.n : (rb.raw ? 1 : 2) * g.batch * g.n * k_pad);
     float* scratch = nullptr;
     if (a_floats + b_floats > 0) TRS_TRY(malloc_on_stream(stream, (size_t)(a_floats + b_floats) * sizeof(float), (void**)&scratch));
-    struct ScratchGuard {       // handed back at once: reuse is ordered behind this stream's work
-        trs_stream s; void* p;
-        ~ScratchGuard() { if (p) free_on_stream(s, p); }
-    } scratch_guard{stream, scratch};
+    ScratchGuard scratch_guard{stream, scratch};
     // scratch layout: [A lo | A hi (re-laid only)] [B lo | B hi (re-laid only)]
     float* a_lo = scratch;
     float* a_hi = a_lo + g.batch * g.m * k_pad;
@@ -1059,23 +1109,40 @@ int32_t gemm_tc_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, tr
     const long long total_tiles = tiles_m * tiles_n * g.batch;
     if (total_tiles > INT32_MAX) return fail(TRS_ERR_UNSUPPORTED, "too many output tiles");
     EpilogueArgs e{g.c, g.bias, g.aux, g.preact, g.c_batch_stride, g.c_row_stride, (int)g.m, (int)g.n, (int)(k_pad / bk), g.epilogue,
-                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles, ra.mn ? 1 : 0, rb.mn ? 1 : 0,
+                   (int)tiles_m, (int)tiles_n, (int)total_tiles, (int)total_tiles, (int)total_tiles, 1, nullptr, nullptr, ra.mn ? 1 : 0, rb.mn ? 1 : 0,
                    planes ? planes->c_lo : nullptr, planes ? planes->c_flag : nullptr, words->error, WAIT_CYCLES};
     // units that work side by side: SMs, or resident CTA pairs
     const long long units = pair ? words->pair_clusters : sm_count(stream->device);
-    // A last round that occupies at most half of the units is cut in two along K (plain products on
-    // a dense C only): 512 tiles on 148 SMs then take 3.5 instead of 4 tile times.
+    // The last round of tiles rarely fills the GPU (128 tile pairs on 74 SM pairs: 74 + 54).  Its tiles are cut
+    // into `parts` items along K when that shortens the round: with p parts the round takes ceil(tail * p / units) / p
+    // tile times, plus a little per part for writing and adding up partial sums.
     const long long tail = total_tiles % units;
-    const bool dense_c = g.c_row_stride == g.n && (g.batch == 1 || g.c_batch_stride == g.m * g.n);
-    if (g.epilogue == TRS_EPI_NONE && !e.c_lo && total_tiles > units && tail > 0 && tail * 2 <= units && e.k_blocks >= 16 && dense_c) {
+    int parts = 1;
+    if (tail > 0) {
+        double best = 1.0;
+        for (int p = 2; p <= 8 && e.k_blocks / p >= 4; ++p) {
+            const double t = (double)((tail * p + units - 1) / units) / p + 0.03 * (p - 1);
+            if (t < best - 0.05) { best = t; parts = p; }
+        }
+    }
+    ScratchGuard partial_guard{stream, nullptr};
+    if (parts > 1) {
+        const size_t slabs = (size_t)tail * (size_t)(tile_rows / 32);
+        const size_t counter_bytes = (slabs * sizeof(unsigned int) + 511) & ~size_t(511);
+        const size_t partial_bytes = (size_t)tail * parts * (size_t)tile_rows * BN * sizeof(float);
+        void* block = nullptr;
+        TRS_TRY(malloc_on_stream(stream, counter_bytes + partial_bytes, &block));
+        partial_guard.p = block;
+        e.arrivals = reinterpret_cast<unsigned int*>(block);
+        e.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(block) + counter_bytes);
+        e.parts = parts;
         e.whole_tiles = (int)(total_tiles - tail);
-        e.total_items = (int)(e.whole_tiles + 2 * tail);
-        TRS_CUDA(cudaMemsetAsync(g.c, 0, (size_t)(g.batch * g.m * g.n) * sizeof(float), stream->stream));
+        e.total_items = (int)(e.whole_tiles + parts * tail);
+        TRS_CUDA(cudaMemsetAsync(e.arrivals, 0, counter_bytes, stream->stream));
     }
     const unsigned grid = (unsigned)std::min<long long>(e.total_items, units);
-    const bool zeroed_c = e.total_items != e.total_tiles;       // a memset of C sits between the preparation and this kernel
-    if (zeroed_c) {
-        // ordinary launch: programmatic serialization is between kernels only
+    if (parts > 1) {
+        // ordinary launch behind the memset of the counters: programmatic serialization is between kernels only
         if (pair) gemm_tf32x3_pair_kernel<<<2 * grid, 192, PAIR_SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
         else gemm_tf32x3_kernel<<<grid, 192, SMEM_BYTES, stream->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, e);
         TRS_CUDA(cudaGetLastError());

@@ -275,7 +275,7 @@ struct Params {
 // Reference semantics (pytorch-rs src/tensor.rs:4388-4432): exact zeros keep their sign through
 // relu, relu(NaN) is +0, the relu VJP passes the upstream for NaN or strictly positive inputs.
 __device__ __forceinline__ float trs_relu(float v) {
-    return ((__float_as_uint(v) & 0x7fffffffu) == 0u) ? v : fmaxf(v, 0.0f);
+    return (__float_as_uint(v) == 0x80000000u) ? v : fmaxf(v, 0.0f);      // fmaxf already keeps +0 and sends NaN to +0; only -0 needs the pass-through
 }
 __device__ __forceinline__ float trs_relu_vjp(float x, float g) {
     u32 b = __float_as_uint(x), mag = b & 0x7fffffffu;
@@ -286,27 +286,45 @@ __device__ __forceinline__ float trs_sqrt(float v) {
     u32 b = __float_as_uint(v), mag = b & 0x7fffffffu;
     return ((b >> 31) != 0u && mag != 0u && mag <= 0x7f800000u) ? __uint_as_float(0x7fc00000u) : __fsqrt_rn(v);
 }
-// exp within 1 ulp of a correctly rounded expf (the reference calls the platform's libm expf, src/tensor.rs:2398-2400;
-// glibc's is within 0.502 ulp of the true value, CUDA's expf only within 2).  Cody-Waite reduction x = j ln2 + r with
-// ln2 in two parts, |r| <= ln2/2, exp(r) = 1 + r + r^2 q(r) with a degree-4 minimax q (error 3e-9), result scaled by
-// 2^j in two exact-or-once-rounded steps so that subnormal results round once.  Checked against glibc expf on every
-// float32 in [-104.5, 89.5]: never more than 1 ulp apart, 99.2 % of the inputs bit-equal.  exp(+-0) = exp(+-denormal)
-// = 1, exp(x > 88.73) = +inf, exp(x < -103.98) = +0, NaN stays NaN (the clamp's comparisons are false for it).
-__device__ __forceinline__ float trs_exp(float x) {
-    const float t = x < -110.0f ? -110.0f : (x > 90.0f ? 90.0f : x);
-    const float j = __fsub_rn(__fmaf_rn(t, 1.44269502f, 12582912.0f), 12582912.0f);    // nearest integer to t / ln2
+// exp within 1 ulp of glibc's expf (the reference calls the platform's libm expf, src/tensor.rs:2398-2400; glibc's is
+// within 0.502 ulp of the true value, CUDA's expf only within 2).  Cody-Waite reduction x = j ln2 + r with ln2 in two
+// parts, |r| <= ln2/2, exp(r) as a degree-6 polynomial (minimax, error 3e-9) in Horner form, scaled by 2^j.  For
+// |x| <= 87 the result is a normal number and the scaling is an add into the exponent field (j sits in the low
+// mantissa bits of the rounding constant's sum); everything else -- overflow, subnormal results, inf, NaN -- takes
+// the out-of-line path, which scales in two steps so that a subnormal result is rounded once.  Checked against glibc
+// expf on every float32 in [-104.5, 89.5]: never more than 1 ulp apart.  exp(+-0) = exp(+-denormal) = 1,
+// exp(x > 88.73) = +inf, exp(x < -103.98) = +0, NaN stays NaN.
+__device__ __noinline__ float trs_exp_slow(float x) {
+    const float t = x < -110.0f ? -110.0f : (x > 90.0f ? 90.0f : x);      // false for NaN: it passes through
+    const float j = __fsub_rn(__fmaf_rn(t, 1.44269502f, 12582912.0f), 12582912.0f);
     float r = __fmaf_rn(j, -0.693145752f, t);
+    r = __fmaf_rn(j, -1.42860677e-06f, r);
+    float q = __uint_as_float(0x3ab6da3fu);
+    q = __fmaf_rn(q, r, __uint_as_float(0x3c091dc9u));
+    q = __fmaf_rn(q, r, __uint_as_float(0x3d2aaa2fu));
+    q = __fmaf_rn(q, r, __uint_as_float(0x3e2aaa47u));
+    q = __fmaf_rn(q, r, 0.5f);
+    q = __fmaf_rn(q, r, 1.0f);
+    const float p = __fmaf_rn(q, r, 1.0f);
+    const int ji = __float2int_rn(j);                     // 0 for NaN
+    const int h = ji >> 1;
+    const float s1 = __uint_as_float((u32)(h + 127) << 23), s2 = __uint_as_float((u32)(ji - h + 127) << 23);
+    return __fmul_rn(__fmul_rn(p, s1), s2);
+}
+__device__ __forceinline__ float trs_exp(float x) {
+    if (!(fabsf(x) <= 87.0f)) return trs_exp_slow(x);
+    const float m = __fmaf_rn(x, 1.44269502f, 12582912.0f);       // 1.5 * 2^23 + nearest integer to x / ln2
+    const float j = __fsub_rn(m, 12582912.0f);
+    float r = __fmaf_rn(j, -0.693145752f, x);
     r = __fmaf_rn(j, -1.42860677e-06f, r);
     float q = __uint_as_float(0x3ab6da3fu);               // 0x1.6db47ep-10
     q = __fmaf_rn(q, r, __uint_as_float(0x3c091dc9u));    // 0x1.123b92p-7
     q = __fmaf_rn(q, r, __uint_as_float(0x3d2aaa2fu));    // 0x1.55545ep-5
     q = __fmaf_rn(q, r, __uint_as_float(0x3e2aaa47u));    // 0x1.55548ep-3
     q = __fmaf_rn(q, r, 0.5f);
-    const float p = __fadd_rn(__fmaf_rn(q, __fmul_rn(r, r), r), 1.0f);
-    const int ji = __float2int_rn(j);                     // 0 for NaN
-    const int h = ji >> 1;
-    const float s1 = __uint_as_float((u32)(h + 127) << 23), s2 = __uint_as_float((u32)(ji - h + 127) << 23);
-    return __fmul_rn(__fmul_rn(p, s1), s2);
+    q = __fmaf_rn(q, r, 1.0f);
+    const float p = __fmaf_rn(q, r, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(m) << 23));
 }
 __device__ __forceinline__ u32 trs_div(u32 n, u32 magic, u32 shift) { return (__umulhi(n, magic) + n) >> shift; }
 )SRC";
