@@ -193,6 +193,8 @@ class Bench:
         self.torch, self.tdist = torch, tdist
         self.rank, self.world, self.local_rank = rank, world, local_rank
         self.dev = f"cuda:{local_rank}"
+        from torch_rs import _abi
+        _abi.check(_abi.lib().trs_set_current_device(local_rank))      # pinned staging memory belongs to this rank's GPU context
         self.numa_node = tdist.bind_to_device_numa_node(local_rank)     # staging memory local to this GPU's PCIe root
         if world > 1:
             tdist.init_process_group("nccl")       # gloo control plane + the engine's own NCCL communicator

@@ -138,6 +138,12 @@ typedef struct trs_gemm_desc {
  * New relative to the reference, whose Device has the single variant Cpu (src/device.rs:5-9)
  * and whose Storage owns a Vec<f32> (src/storage.rs:7-18, 116-134). */
 int32_t trs_device_count(int32_t* count);
+/* Makes `device` the calling thread's current CUDA device.  Every entry point that takes a stream or a device
+ * selects that device itself for the duration of the call; this only decides where resources that name no
+ * device land (page-locked host memory from trs_malloc_host).  A process that follows the reference's LOCAL_RANK
+ * convention (python/torch_rs/distributed/distributed_c10d.py:71-72) calls it once with that rank, so that it
+ * never creates a context on another rank's GPU. */
+int32_t trs_set_current_device(int32_t device);
 /* PCI bus id ("0000:1b:00.0") of a device, for placing host staging memory on the device's NUMA node. */
 int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length);
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr);       /* cached blocks; Storage::from_owned */

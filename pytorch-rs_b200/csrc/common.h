@@ -16,7 +16,8 @@ struct trs_stream_s {
     cudaStream_t stream;
 };
 struct trs_event_s {
-    cudaEvent_t event;
+    cudaEvent_t event;     // created on the device of the first stream it is recorded on (an event belongs to one device)
+    int device;            // -1 until then
 };
 
 namespace trs {

@@ -84,6 +84,13 @@ int32_t trs_device_count(int32_t* count) {
     return TRS_OK;
 }
 
+int32_t trs_set_current_device(int32_t device) {
+    if (device < 0 || device >= kMaxDevices) return fail(TRS_ERR_INVALID_ARGUMENT, "bad device %d", device);
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(e, "cudaSetDevice"); }
+    return TRS_OK;
+}
+
 int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length) {
     if (!buffer || length < 16) return fail(TRS_ERR_INVALID_ARGUMENT, "buffer of at least 16 bytes needed");
     TRS_CUDA(cudaDeviceGetPCIBusId(buffer, length, device));
@@ -250,9 +257,7 @@ int32_t trs_device_sync(int32_t device) {
 
 int32_t trs_event_create(trs_event* event) {
     if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
-    cudaEvent_t e;
-    TRS_CUDA(cudaEventCreate(&e));
-    *event = new trs_event_s{e};
+    *event = new trs_event_s{nullptr, -1};
     return TRS_OK;
 }
 
@@ -260,25 +265,36 @@ int32_t trs_event_record(trs_event event, trs_stream stream) {
     TRS_TRY(check_stream(stream));
     if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
     DeviceGuard guard(stream->device);
+    if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", stream->device);
+    if (event->device != stream->device) {
+        // a CUDA event belongs to the device that was current when it was created: (re)create it where it is used
+        if (event->event) cudaEventDestroy(event->event);
+        event->event = nullptr;
+        event->device = -1;
+        TRS_CUDA(cudaEventCreate(&event->event));
+        event->device = stream->device;
+    }
     TRS_CUDA(cudaEventRecord(event->event, stream->stream));
     return TRS_OK;
 }
 
 int32_t trs_event_sync(trs_event event) {
     if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    if (!event->event) return TRS_OK;                    // never recorded: nothing to wait for
     TRS_CUDA(cudaEventSynchronize(event->event));
     return TRS_OK;
 }
 
 int32_t trs_event_elapsed_ms(trs_event start, trs_event stop, float* ms) {
     if (!start || !stop || !ms) return fail(TRS_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (!start->event || !stop->event) return fail(TRS_ERR_INVALID_ARGUMENT, "both events must have been recorded");
     TRS_CUDA(cudaEventElapsedTime(ms, start->event, stop->event));
     return TRS_OK;
 }
 
 int32_t trs_event_destroy(trs_event event) {
     if (!event) return TRS_OK;
-    cudaEventDestroy(event->event);
+    if (event->event) cudaEventDestroy(event->event);
     delete event;
     return TRS_OK;
 }
@@ -286,6 +302,7 @@ int32_t trs_event_destroy(trs_event event) {
 int32_t trs_stream_wait_event(trs_stream stream, trs_event event) {
     TRS_TRY(check_stream(stream));
     if (!event) return fail(TRS_ERR_INVALID_ARGUMENT, "event is NULL");
+    if (!event->event) return TRS_OK;                    // never recorded: nothing to wait for
     DeviceGuard guard(stream->device);
     TRS_CUDA(cudaStreamWaitEvent(stream->stream, event->event, 0));
     return TRS_OK;

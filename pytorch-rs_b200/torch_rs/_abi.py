@@ -61,6 +61,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 # name -> argtypes (restype is int32 status unless listed in _SPECIAL)
 _PROTOTYPES = {
     "trs_device_count": [ctypes.POINTER(ctypes.c_int32)],
+    "trs_set_current_device": [ctypes.c_int32],
     "trs_device_pci_bus_id": [ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32],
     "trs_malloc": [ctypes.c_int32, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)],
     "trs_free": [ctypes.c_int32, ctypes.c_void_p],

@@ -54,6 +54,9 @@ def init_process_group(backend: str | None = None) -> str:
     if not dist.is_initialized():
         dist.init_process_group("gloo")
     _state.update(initialized=True, backend=backend)
+    if backend == "nccl":
+        from . import _abi
+        _abi.check(_abi.lib().trs_set_current_device(get_node_local_rank(0)))    # this process works on its own GPU only
     if backend == "nccl" and get_world_size() > 1:
         import ctypes
         from . import _host

@@ -67,10 +67,20 @@ def gpu_main(out_path):
         return loss, (W1, W2, B1)
 
     begin, end = dist.shard_bounds(bsz, rank, world)
-    loss, params = step(slice(begin, end))
-    dist.all_reduce_gradients(params)
+    # several steps back to back: each exchange runs on the side stream under the next kernels, so a missing
+    # ordering would show as a step whose gradients differ from the first one's
+    history = []
+    for _ in range(4):
+        loss, params = step(slice(begin, end))
+        dist.all_reduce_gradients(params)
+        history.append([p.grad.numpy() for p in params])
+    repeatable = all(np.array_equal(a.view(np.uint32), b.view(np.uint32)) for later in history[1:] for a, b in zip(history[0], later))
     total_loss = dist.all_reduce_host(np.array([loss.item()], dtype=np.float64))[0]
-    grads = [p.grad.numpy() for p in params]
+    grads = history[-1]
+    # one tensor summed in place over the ranks, and a value derived from it afterwards
+    t = torch.tensor(np.full((3, 5), float(rank + 1), dtype=np.float32), device=dev)
+    dist.all_reduce_(t)
+    summed_ok = bool(np.array_equal((t * 2.0).numpy(), np.full((3, 5), 2.0 * sum(range(1, world + 1)), dtype=np.float32)))
     if rank == 0:
         full_loss, full_params = step(slice(0, bsz))
         worst = 0.0
@@ -78,7 +88,8 @@ def gpu_main(out_path):
             want = p.grad.numpy().astype(np.float64)
             rms = np.sqrt(np.mean(want ** 2))
             worst = max(worst, float(np.max(np.abs(g - want) / (1e-5 * np.sqrt(bsz) * np.maximum(np.abs(want), rms) + 1e-30))))
-        json.dump({"world": world, "worst_error_over_bound": worst, "loss": float(total_loss), "full_loss": float(full_loss.item())},
+        json.dump({"world": world, "worst_error_over_bound": worst, "loss": float(total_loss), "full_loss": float(full_loss.item()),
+                   "repeatable": bool(repeatable), "all_reduce_in_place_ok": summed_ok},
                   open(out_path, "w"))
     dist.barrier()
     dist.destroy_process_group()

@@ -67,6 +67,7 @@ def test_data_parallel_mlp_gradients_match_single_gpu(tmp_path):
     r = launch("gpu", tmp_path)
     assert r["world"] == 2
     assert r["worst_error_over_bound"] <= 1.0
+    assert r["repeatable"] and r["all_reduce_in_place_ok"]
     assert abs(r["loss"] - r["full_loss"]) <= 1e-4 * abs(r["full_loss"]) + 1e-3
 
 
