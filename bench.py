@@ -798,6 +798,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 def main():
+    global MIN_REGION_SECONDS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -813,7 +814,6 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the copy ceiling and configs 1, 3, 4, 5")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    global MIN_REGION_SECONDS
     MIN_REGION_SECONDS = args.min_seconds
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

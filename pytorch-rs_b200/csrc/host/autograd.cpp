@@ -6,6 +6,7 @@
 #include "autograd.h"
 
 #include <algorithm>
+#include <atomic>
 #include <unordered_map>
 #include <unordered_set>
 
@@ -210,6 +211,23 @@ TensorP grad_of(const TensorP& t) {
     return t->meta->grad;
 }
 
+// Evaluates a leaf's finished gradient (contiguous, in a buffer of its own) and, for a first gradient, records the
+// event a gradient exchange on another stream waits for.
+static std::atomic<uint64_t> g_ready_counter{0};
+static void finish_leaf_gradient(std::pair<AutogradMeta*, TensorP>& entry, int device) {
+    AutogradMeta* m = entry.first;
+    TensorP g = entry.second;
+    if (!layout_is_contiguous(g->v.shape, g->v.strides)) g = contiguous(g);
+    if (!m->grad && !g->v.st->node && g->v.st.use_count() > 1) g = contiguous_result(TRS_OP_COPY, {g->v}, g->v.shape, device);
+    materialize(g->v.st);
+    if (!m->grad) {
+        if (!m->grad_ready) check_cuda(trs_event_create(&m->grad_ready), "creating the gradient event");
+        check_cuda(trs_event_record(m->grad_ready, stream_for(device)), "recording the gradient event");
+        m->ready_order = ++g_ready_counter;
+    }
+    entry.second = g;
+}
+
 // Moves the parents of a recorded op out of it, so that releasing the op does not release them.
 static void take_parents(const std::shared_ptr<GradFn>& fn, std::vector<std::shared_ptr<AutogradMeta>>& pending) {
     if (!fn || fn.use_count() != 1) return;
@@ -280,16 +298,10 @@ void backward(const TensorP& root) {
         TensorP g = found->second;
         grads.erase(found);
         if (m->leaf) {
-            // Every contribution to this leaf has been recorded: run its kernels now rather than at the end, so
-            // that a gradient exchange on another stream can start under the rest of the backward pass.
-            if (!layout_is_contiguous(g->v.shape, g->v.strides)) g = contiguous(g);
-            if (!m->grad && !g->v.st->node && g->v.st.use_count() > 1) g = contiguous_result(TRS_OP_COPY, {g->v}, g->v.shape, device);
-            materialize(g->v.st);
-            if (!m->grad) {
-                if (!m->grad_ready) check_cuda(trs_event_create(&m->grad_ready), "creating the gradient event");
-                check_cuda(trs_event_record(m->grad_ready, stream_for(device)), "recording the gradient event");
-            }
+            // Every contribution to this leaf has been recorded.  A cheap gradient (a fused chain, a reduction) is
+            // evaluated now; one that is still an unevaluated product waits for the end of the walk (see below).
             leaf_grads.emplace_back(m, g);
+            if (!(g->v.st->node && g->v.st->node->op == OP_MATMUL)) finish_leaf_gradient(leaf_grads.back(), device);
             continue;
         }
         const GradFn& fn = *m->grad_fn;
@@ -300,6 +312,17 @@ void backward(const TensorP& root) {
             auto have = grads.find(target);
             grads[target] = accumulate(have == grads.end() ? nullptr : have->second, contributions[i], device);
         }
+    }
+
+    // Weight gradients that are still unevaluated products run now, the largest first: a data-parallel host sums
+    // each gradient over the ranks on a side stream as soon as its kernel has finished (all_reduce_grads), so the
+    // exchange of a large gradient runs under the products that follow it and only the smallest one's is exposed.
+    {
+        std::vector<size_t> deferred;
+        for (size_t i = 0; i < leaf_grads.size(); ++i)
+            if (leaf_grads[i].second->v.st->node) deferred.push_back(i);
+        std::stable_sort(deferred.begin(), deferred.end(), [&](size_t a, size_t b) { return leaf_grads[a].second->numel > leaf_grads[b].second->numel; });
+        for (size_t i : deferred) finish_leaf_gradient(leaf_grads[i], device);
     }
 
     // Every VJP has been enqueued without error: commit (src/tensor.rs:2918-2938).  Leaf
@@ -316,6 +339,7 @@ void backward(const TensorP& root) {
                                           stream_for(device)), "leaf gradient accumulation");
             if (!leaf->grad_ready) check_cuda(trs_event_create(&leaf->grad_ready), "creating the gradient event");
             check_cuda(trs_event_record(leaf->grad_ready, stream_for(device)), "recording the gradient event");
+            leaf->ready_order = ++g_ready_counter;
         }
     }
     for (AutogradMeta* m : visited_nodes)

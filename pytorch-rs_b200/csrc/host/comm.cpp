@@ -8,6 +8,7 @@
 #include "autograd.h"
 #include "engine.h"
 
+#include <algorithm>
 #include <map>
 
 namespace trsh {
@@ -68,8 +69,12 @@ void all_reduce_grads(const std::vector<TensorP>& leaves) {
     std::lock_guard<std::recursive_mutex> lock(g_engine_mu);
     if (!g_comm.comm || g_comm.size == 1) return;
     bool any = false;
-    for (const TensorP& leaf : leaves) {
-        if (!leaf || !leaf->meta || !leaf->meta->leaf || !leaf->meta->grad) continue;
+    // in the order the gradients became ready on the compute stream, whatever order the caller names them in
+    std::vector<TensorP> ordered;
+    for (const TensorP& leaf : leaves)
+        if (leaf && leaf->meta && leaf->meta->leaf && leaf->meta->grad) ordered.push_back(leaf);
+    std::stable_sort(ordered.begin(), ordered.end(), [](const TensorP& a, const TensorP& b) { return a->meta->ready_order < b->meta->ready_order; });
+    for (const TensorP& leaf : ordered) {
         Tensor& g = *leaf->meta->grad;
         if (g.device() != g_comm.device) throw Error(ErrKind::DeviceMismatch, "gradient lives on another device than the communicator");
         if (g.numel == 0) continue;

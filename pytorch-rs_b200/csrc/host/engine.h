@@ -107,6 +107,7 @@ struct AutogradMeta {
     // leaf: recorded on the compute stream right behind the kernel that produced the latest gradient, so that a
     // gradient all-reduce on another stream can start while the rest of the backward pass still runs
     trs_event grad_ready = nullptr;
+    uint64_t ready_order = 0;                 // position of that event among all gradient events of the process
     // Releases a chain of recorded ops with a loop, not by recursion (the reference's iterative Drop,
     // src/tensor.rs:189-206): a 100,000-op chain must not overflow the stack when its last handle goes.
     ~AutogradMeta();

@@ -109,6 +109,71 @@ def test_layout_planner_reference_goldens():
     assert b"The size of tensor a (0) must match the size of tensor b (2) at non-singleton dimension 0" in lib.trsh_last_error()
 
 
+def test_layout_planner_remaining_reference_stride_goldens():
+    """Every stride case the reference's own tests hold for this path, asserted on the host planner itself (the
+    planner and the CPU checker's planner are translations of the same rules by the same hand, so comparing them
+    with each other proves little; these vectors are the independent pin): dense views keep their strides through
+    unary / scalar / same-layout binary / row-broadcast ops (tests/tensor_baseline.rs:1606-1658,
+    tests/test_transpose.py:244-259), empty operands (tensor_baseline.rs:2189-2211), a rank-0 operand against a
+    transposed view (tests/autograd.rs:190-218), reflected division (tests/test_transpose.py:288-313)."""
+    import json
+    lib = _host.lib()
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+
+    def unary(shape, strides):
+        out = _arr([0] * max(len(shape), 1))
+        assert lib.trsh_plan_unary(len(shape), _arr(shape), _arr(strides), out) == 0
+        return list(out)[:len(shape)]
+
+    def scalar(shape, strides):
+        out = _arr([0] * max(len(shape), 1))
+        status = lib.trsh_plan_scalar(len(shape), _arr(shape), _arr(strides), out)
+        return list(out)[:len(shape)] if status == 0 else status
+
+    def binary(ls, lst, rs, rst):
+        rank = ctypes.c_int32()
+        oshape, ostrides = _arr([0] * 8), _arr([0] * 8)
+        assert lib.trsh_plan_binary(len(ls), _arr(ls), _arr(lst), len(rs), _arr(rs), _arr(rst), ctypes.byref(rank), oshape, ostrides) == 0
+        return list(oshape)[:rank.value], list(ostrides)[:rank.value]
+
+    def contiguous(shape):
+        strides, s = [0] * len(shape), 1
+        for axis in range(len(shape) - 1, -1, -1):
+            strides[axis] = s
+            s *= max(shape[axis], 1)
+        return strides
+
+    g = gold["strides"]["unary_keeps_dense_view"]
+    shape, strides = g["view_shape"], g["view_strides"]
+    assert unary(shape, strides) == strides                                   # relu / sin / exp
+    assert scalar(shape, strides) == strides                                  # view + 2.0
+    assert binary(shape, strides, shape, strides) == (shape, strides)         # view + view
+    assert binary(shape, strides, [2], [1]) == (shape, strides)               # view + row of two
+    transposed = ([4, 3], [1, 4])                                            # the rank-2 slice of the same test
+    assert unary(*transposed) == transposed[1]
+    g = gold["strides"]["singleton_channels_last"]
+    assert binary(g["view_shape"], g["view_strides"], g["view_shape"], g["view_strides"])[1] == g["expected"]
+    for case in gold["strides"]["empty_binary"]["cases"]:
+        assert binary(case["left"], contiguous(case["left"]), case["right"], contiguous(case["right"])) == (case["shape"], case["expected"])
+    c = gold["strides"]["empty_binary"]["chained_relu_after_scalar"]
+    after_scalar = scalar(c["shape"], contiguous(c["shape"]))
+    assert after_scalar == c["scalar_strides"] and unary(c["shape"], after_scalar) == c["relu_strides"]
+    g = gold["strides"]["rank_zero_mul_view"]
+    assert binary(g["view_shape"], g["view_strides"], [], []) == (g["view_shape"], g["expected"])
+    assert binary([], [], g["view_shape"], g["view_strides"]) == (g["view_shape"], g["expected"])
+
+    # reflected division is planned as reciprocal (a unary op) followed by a scalar op (src/tensor.rs:2324-2363)
+    d = gold["reflected_division"]
+    view = d["view"]
+    assert scalar(view["shape"], view["strides"]) == d["div_one_strides"]
+    assert scalar(view["shape"], unary(view["shape"], view["strides"])) == d["reflected_strides"]
+    for case in d["empty_cases"] + [d["large"]]:
+        assert scalar(case["shape"], unary(case["shape"], case["strides"])) == case["expected"]
+    e = d["extreme_transposed"]
+    out = _arr([0] * 3)
+    assert lib.trsh_plan_unary(3, _arr(e["shape"]), _arr(e["strides"]), out) == 11           # StrideCalculationOverflow
+
+
 def test_layout_planner_extreme_empty_goldens():
     import json
     lib = _host.lib()
