@@ -1,6 +1,9 @@
 // Fused pointwise chains: plan -> specialised kernel (NVRTC, cached) -> launch.
 // Also the small fixed kernels for fill and in-place accumulation.
 #include <nvrtc.h>
+#include <unistd.h>
+
+#include <cstdlib>
 
 #include <mutex>
 #include <unordered_map>
@@ -46,6 +49,61 @@ int32_t compile_cubin(const std::string& source, std::string* cubin) {
     return TRS_OK;
 }
 
+// ---- optional cache of compiled chains on disk -------------------------------------------------------
+// Specialising a chain costs about 150 ms for the first one of a process (NVRTC start-up included) and 50-60 ms
+// for each further one.  A process that names a directory in TRS_JIT_CACHE_DIR keeps the compiled code there and
+// later processes read it back instead of compiling.  A file is named by a 64-bit hash of the generated source and
+// holds a second hash and the source length, which must match too; it is written under a temporary name and
+// renamed, so a reader never sees half a file.  Without the variable nothing touches the disk.
+uint64_t fnv1a(const std::string& text, uint64_t seed) {
+    uint64_t h = 1469598103934665603ull ^ seed;
+    for (unsigned char c : text) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
+struct DiskHeader {
+    uint64_t magic, check, source_length, cubin_length;
+};
+constexpr uint64_t kDiskMagic = 0x31303062754a5254ull;      // "TRJub001"
+
+std::string disk_path(const std::string& source) {
+    const char* dir = getenv("TRS_JIT_CACHE_DIR");
+    if (!dir || !*dir) return std::string();
+    char name[64];
+    snprintf(name, sizeof name, "/trs_pw_%016llx.cubin", (unsigned long long)fnv1a(source, 0));
+    return std::string(dir) + name;
+}
+
+bool disk_load(const std::string& source, std::string* cubin) {
+    const std::string path = disk_path(source);
+    if (path.empty()) return false;
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    DiskHeader h{};
+    bool ok = fread(&h, sizeof h, 1, f) == 1 && h.magic == kDiskMagic && h.check == fnv1a(source, 0x9e3779b97f4a7c15ull) &&
+              h.source_length == source.size() && h.cubin_length > 0 && h.cubin_length < (64u << 20);
+    if (ok) {
+        cubin->resize(h.cubin_length);
+        ok = fread(&(*cubin)[0], 1, h.cubin_length, f) == h.cubin_length;
+    }
+    fclose(f);
+    if (!ok) cubin->clear();
+    return ok;
+}
+
+void disk_store(const std::string& source, const std::string& cubin) {
+    const std::string path = disk_path(source);
+    if (path.empty()) return;
+    char suffix[32];
+    snprintf(suffix, sizeof suffix, ".tmp%ld", (long)getpid());
+    const std::string tmp = path + suffix;
+    FILE* f = fopen(tmp.c_str(), "wb");
+    if (!f) return;                                   // an unwritable directory only means no cache
+    DiskHeader h{kDiskMagic, fnv1a(source, 0x9e3779b97f4a7c15ull), source.size(), cubin.size()};
+    const bool ok = fwrite(&h, sizeof h, 1, f) == 1 && fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+    if (fclose(f) != 0 || !ok || rename(tmp.c_str(), path.c_str()) != 0) remove(tmp.c_str());
+}
+
 // Returns the cache entry of this chain and plan, generating and compiling its source if needed; loads
 // it onto the GPU when `load` is set (loading needs a device, compiling does not).
 int32_t get_kernel(const trs_program* program, const PwPlan& plan, bool load, JitEntry** out) {
@@ -53,8 +111,12 @@ int32_t get_kernel(const trs_program* program, const PwPlan& plan, bool load, Ji
     std::lock_guard<std::mutex> lock(g_jit_mu);
     JitEntry& e = g_jit_cache[key];
     if (e.cubin.empty()) {
-        int32_t s = compile_cubin(pw_generate_source(program, plan), &e.cubin);
-        if (s != TRS_OK) { g_jit_cache.erase(key); return s; }
+        const std::string source = pw_generate_source(program, plan);
+        if (!disk_load(source, &e.cubin)) {
+            int32_t s = compile_cubin(source, &e.cubin);
+            if (s != TRS_OK) { g_jit_cache.erase(key); return s; }
+            disk_store(source, e.cubin);
+        }
     }
     if (load && !e.kernel) {
         cudaError_t err = cudaLibraryLoadData(&e.library, e.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);

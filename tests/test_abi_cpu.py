@@ -172,3 +172,32 @@ def test_collective_and_stream_ordered_entry_points_check_their_arguments():
     assert lib.trs_free_async(0, None, None) == 1
     assert lib.trs_debug_wait_probe(None, 1000) == 1
     assert lib.trs_split_lo_f32(None, 4, None, None, None) == 1
+
+
+def test_compiled_chains_can_be_kept_on_disk(tmp_path):
+    """TRS_JIT_CACHE_DIR: a second process reads the compiled chain back instead of compiling it (no GPU needed)."""
+    import subprocess
+    import sys
+    import time
+    script = (
+        "import ctypes, sys, time; sys.path.insert(0, %r); from torch_rs import _abi\n"
+        "prog = _abi.make_program(1, [('sin', 0, 0, 0), ('exp', 1, 0, 0), ('relu', 2, 0, 0)], [3])\n"
+        "ins = (_abi.Operand * 1)(_abi.make_operand(0x10000000, 0, [77, 33], [33, 1]))\n"
+        "outs = (_abi.Operand * 1)(_abi.make_operand(0x50000000, 0, [77, 33], [33, 1]))\n"
+        "k = ctypes.create_string_buffer(16)\n"
+        "t = time.perf_counter(); s = _abi.lib().trs_pointwise_prepare(prog, ins, outs, k); print(s, (time.perf_counter() - t) * 1e3)\n"
+    ) % os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "pytorch-rs_b200")
+    env = dict(os.environ, TRS_JIT_CACHE_DIR=str(tmp_path))
+    first = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=120)
+    assert first.returncode == 0 and first.stdout.split()[0] == "0", first.stderr
+    files = [f for f in os.listdir(tmp_path) if f.endswith(".cubin")]
+    assert len(files) == 1
+    second = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=120)
+    assert second.returncode == 0 and second.stdout.split()[0] == "0", second.stderr
+    assert float(second.stdout.split()[1]) < 0.5 * float(first.stdout.split()[1])      # no compilation the second time
+    # a damaged file is ignored and replaced
+    path = os.path.join(tmp_path, files[0])
+    open(path, "r+b").write(b"garbage!")
+    third = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=120)
+    assert third.returncode == 0 and third.stdout.split()[0] == "0", third.stderr
+    assert open(path, "rb").read(8) != b"garbage!"
