@@ -287,8 +287,10 @@ template <bool kPair>
 __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_t tmem_acc, long long row, long long batch_off, int tile_n,
                                                   int part, int cut, int slab, bool vec_ok, int lane, uint32_t empty_bar_addr) {
     constexpr int kTileRows = kPair ? 2 * BM : BM;
+    // partial sums of a slab: [32-column chunk][group of 4 columns][lane][4 floats], so that the 32 lanes of a warp
+    // write (and the finishing warp reads) 512 consecutive bytes per instruction
     float* my_partial = nullptr;
-    if (part >= 0) my_partial = e.partials + (((long long)cut * e.parts + part) * kTileRows + slab * 32 + lane) * BN;
+    if (part >= 0) my_partial = e.partials + (((long long)cut * e.parts + part) * kTileRows + slab * 32) * BN + lane * 4;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -311,7 +313,7 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_
         const long long col0 = (long long)tile_n * BN + c0;
         if (part >= 0) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(my_partial + c0 + j), make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+            for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(my_partial + (c0 + j) * 32), make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
             continue;
         }
         if (row < e.m && col0 < e.n) {
@@ -330,7 +332,7 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_
     earlier = __shfl_sync(0xffffffffu, earlier, 0);
     if (earlier != (unsigned int)(e.parts - 1)) return;
     __threadfence();
-    const float* first = e.partials + (((long long)cut * e.parts) * kTileRows + slab * 32 + lane) * BN;
+    const float* first = e.partials + (((long long)cut * e.parts) * kTileRows + slab * 32) * BN + lane * 4;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
         const long long col0 = (long long)tile_n * BN + c0;
@@ -338,14 +340,14 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs& e, uint32_
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-            const float4 t = __ldcg(reinterpret_cast<const float4*>(first + c0 + j));
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(first + (c0 + j) * 32));
             v[j] = t.x; v[j + 1] = t.y; v[j + 2] = t.z; v[j + 3] = t.w;
         }
         for (int q = 1; q < e.parts; ++q) {                 // fixed order: part 0 + part 1 + ...
             const float* next = first + (long long)q * kTileRows * BN;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-                const float4 t = __ldcg(reinterpret_cast<const float4*>(next + c0 + j));
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(next + (c0 + j) * 32));
                 v[j] = __fadd_rn(v[j], t.x); v[j + 1] = __fadd_rn(v[j + 1], t.y); v[j + 2] = __fadd_rn(v[j + 2], t.z); v[j + 3] = __fadd_rn(v[j + 3], t.w);
             }
         }
@@ -1113,14 +1115,19 @@ int32_t gemm_tc_launch(const trs_gemm_desc& g, const trs_gemm_planes* planes, tr
                    planes ? planes->c_lo : nullptr, planes ? planes->c_flag : nullptr, words->error, WAIT_CYCLES};
     // units that work side by side: SMs, or resident CTA pairs
     const long long units = pair ? words->pair_clusters : sm_count(stream->device);
-    // The last round of tiles rarely fills the GPU (128 tile pairs on 74 SM pairs: 74 + 54).  Its tiles are cut
-    // into `parts` items along K when that shortens the round: with p parts the round takes ceil(tail * p / units) / p
-    // tile times, plus a little per part for writing and adding up partial sums.
+    // The last round of tiles rarely fills the GPU (256 tile pairs on 74 SM pairs: 3 rounds + 34).  Its tiles are cut
+    // into `parts` items along K when that shortens the round: with p parts it takes ceil(tail * p / units) / p tile
+    // times.  A cut item keeps a whole tile's epilogue (drain the accumulator, write 128 KiB per CTA, count itself) and
+    // the finishing item reads every part back, so an item must carry enough MMA work to hide that: at least 2048 of
+    // K per part.  Measured (us, cut / uncut): 4096^3 495 / 510, 512 x 4096 x 4096 97 / 121, 4096 x 4096 x 8192 960 / 1003;
+    // with thinner parts the epilogues become the bottleneck (2048 x 4096 x 4096 cut in four: 317 against 256; 8 x 1024^3 cut
+    // in four: 223 against 88).
     const long long tail = total_tiles % units;
+    const int min_blocks_per_part = 2048 / bk;
     int parts = 1;
     if (tail > 0) {
         double best = 1.0;
-        for (int p = 2; p <= 8 && e.k_blocks / p >= 4; ++p) {
+        for (int p = 2; p <= 8 && e.k_blocks / p >= min_blocks_per_part; ++p) {
             const double t = (double)((tail * p + units - 1) / units) / p + 0.03 * (p - 1);
             if (t < best - 0.05) { best = t; parts = p; }
         }

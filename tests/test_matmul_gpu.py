@@ -258,10 +258,11 @@ def test_batched_product_over_several_rounds_of_tiles():
 
 
 @pytest.mark.parametrize("algo", TC_ALGOS)
-@pytest.mark.parametrize("batch,m,n,k,epilogue", [(8, 1024, 1024, 1024, "bias_relu"),    # 128 tile pairs on 74 SM pairs: 54 cut in four
-                                                   (1, 1024, 1024, 1024, "relu_vjp"),     # fewer tiles than SMs: every tile is cut
+@pytest.mark.parametrize("batch,m,n,k,epilogue", [(1, 1024, 1024, 8192, "bias_relu"),    # fewer tiles than SMs, deep K: every tile is cut in four
+                                                   (1, 1024, 1024, 4096, "relu_vjp"),     # ... in two
                                                    (1, 512, 4096, 4096, "none"),          # one eighth of a 4096^3 product
-                                                   (3, 300, 700, 520, "bias")])           # ragged edges inside cut tiles
+                                                   (2, 300, 700, 6200, "bias"),           # ragged edges inside cut tiles, K tail
+                                                   (8, 1024, 1024, 1024, "bias_relu")])   # shallow K: stays uncut (the parts would be epilogue-bound)
 def test_tiles_cut_along_k_keep_epilogues_and_are_deterministic(algo, batch, m, n, k, epilogue):
     """When the last round of tiles would leave SMs idle its tiles are cut along K; the part that finishes last adds
     the partial sums in part order and applies the epilogue.  The result must not depend on which part finishes
