@@ -159,7 +159,9 @@ def run_reference(args, rank, world):
     from oracle import ref
     ref.build()
     total_steps = args.steps + args.warmup
-    rows = N_SIDE if total_steps * 5.0 <= 150 else 2048
+    # one full-size step takes about 6 s on one core: the whole workload while the run fits in ~2.5 minutes, else as
+    # many of its 8192 physical rows (a multiple of 256) as keep it near 2 minutes
+    rows = N_SIDE if total_steps * 6.0 <= 160 else max(256, min(N_SIDE, int(N_SIDE * 120.0 / (total_steps * 6.0)) // 256 * 256))
     xs, b = make_inputs(0, rows)
     bytes_per_step = 8 * rows * N_SIDE + 4 * rows
     for _ in range(args.warmup):
@@ -527,18 +529,24 @@ def run_c3(bench, args):
     a_host[...] = a[lo:hi]
     b_host[...] = b
 
+    upcoming = [(torch.tensor(a_host, device=dev), torch.tensor(b_host, device=dev))]
+
     def step_e2e():
-        Ad, Bd = torch.tensor(a_host, device=dev), torch.tensor(b_host, device=dev)
-        torch.matmul(Ad, Bd).copy_to_host(c_host, non_blocking=True)
+        Ad, Bd = upcoming[0]
+        product = torch.matmul(Ad, Bd).materialize()
+        upcoming[0] = (torch.tensor(a_host, device=dev), torch.tensor(b_host, device=dev))     # next operands upload under this product
+        product.copy_to_host(c_host, non_blocking=True)
         torch.synchronize(bench.local_rank)
     e2e_ms = bench.time_wall(step_e2e, 5)
+    upcoming.clear()
     e2e_same = None
     if rank == 0:       # same shapes, same tile plan, same rounding order as the resident product
         e2e_same = bool(np.array_equal(c_host[:4].view(np.uint32), held[0].numpy()[:4].view(np.uint32)))
     out["e2e"] = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": 5,
                   "result_equals_device_resident_step": e2e_same,
                   "h2d_bytes_per_step": 4 * ((hi - lo) * n + n * n), "d2h_bytes_per_step": 4 * (hi - lo) * n,
-                  "how": "A shard and B uploaded from pinned host memory, operand images prepared, product, C read back, every step"}
+                  "how": "A shard and B uploaded from pinned host memory, operand images prepared, product, C read back, every step; the next "
+                         "step's operands are uploaded (upload stream) while this step's product runs and its result is read back"}
     for array in (a_host, b_host, c_host):
         torch.pinned_free(array)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -719,9 +727,14 @@ def run_c5(bench, args):
     x_host[...] = x
     g_host = [torch.pinned_empty(4096, 1024), torch.pinned_empty(4096), torch.pinned_empty(4096, 4096)]
 
+    # double-buffered input pipeline: the upload of the next batch is issued (on the engine's upload stream) before this
+    # step's result is awaited, so it runs under this step's kernels; K timed steps contain K uploads
+    upcoming = [torch.tensor(x_host, device=dev)]
+
     def step_e2e():
-        loss, params = mlp_step(torch, torch.tensor(x_host, device=dev), w1, w2, b1)
+        loss, params = mlp_step(torch, upcoming[0], w1, w2, b1)
         tdist.all_reduce_gradients(params)
+        upcoming[0] = torch.tensor(x_host, device=dev)
         for p, dst in zip(params, g_host):
             p.grad.copy_to_host(dst, non_blocking=True)
         held[0] = loss.item()
@@ -729,8 +742,10 @@ def run_c5(bench, args):
     e2e_ms = bench.time_wall(step_e2e, 3, warmup=1)
     out["e2e"] = {"value": C5_FLOPS / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": 3,
                   "h2d_bytes_per_step": 4 * rows * 4096, "d2h_bytes_per_step": 4 * (4096 * 1024 + 4096 + 4096 * 4096) + 4,
-                  "how": "this rank's rows of X uploaded from pinned host memory (the weights stay on the device, as parameters do), "
-                         "forward, backward, gradient all-reduce, the three gradients and the loss read back, every step"}
+                  "how": "this rank's rows of X uploaded from pinned host memory every step (the weights stay on the device, as "
+                         "parameters do), forward, backward, gradient all-reduce, the three gradients and the loss read back; the next "
+                         "batch's upload is issued before the current step's loss is awaited (double buffering), so it overlaps the kernels"}
+    upcoming.clear()
     torch.pinned_free(x_host)
     for array in g_host:
         torch.pinned_free(array)

@@ -51,14 +51,16 @@ bool plane_cache_enabled() { return g_plane_cache; }
 // Blocks come from and go back to the device cache in the order of the engine's compute stream: a block freed
 // here may still be read by kernels already queued on that stream, and the cache hands it to another stream
 // only behind that work.
-float* alloc_floats(i64 count, int device) {
+static float* alloc_floats_on(i64 count, int device, trs_stream stream) {
     void* p = nullptr;
-    int32_t s = trs_malloc_async(device, (size_t)std::max<i64>(count, 1) * sizeof(float), stream_for(device), &p);
+    int32_t s = trs_malloc_async(device, (size_t)std::max<i64>(count, 1) * sizeof(float), stream, &p);
     if (s == TRS_ERR_ALLOCATION_FAILED)
         throw Error(ErrKind::AllocationFailed, "failed to allocate storage for " + std::to_string(count) + " elements");
     check_cuda(s, "device allocation");
     return (float*)p;
 }
+
+float* alloc_floats(i64 count, int device) { return alloc_floats_on(count, device, stream_for(device)); }
 
 void free_floats(int device, void* ptr) {
     if (!ptr) return;
@@ -115,7 +117,7 @@ std::map<int, Egress> g_egress;
 }  // namespace
 
 void sync(int device) {
-    check_cuda(trs_stream_sync(stream_for(device)), "stream sync");
+    check_cuda(trs_stream_sync(stream_for(device)), "stream sync");      // uploads are waited for by this stream already
     auto it = g_egress.find(device);
     if (it != g_egress.end() && it->second.stream) {
         check_cuda(trs_stream_sync(it->second.stream), "egress stream sync");
@@ -159,16 +161,42 @@ TensorP make_tensor(View v) {
     return t;
 }
 
+namespace {
+// Uploads from page-locked memory run on a stream of their own, so that the upload of the next batch proceeds while
+// the kernels of the current one are still running (a host that creates the next input tensor before it waits for
+// the current result gets the overlap; the compute stream only waits for the copy it is about to read).
+struct Ingress {
+    trs_stream stream = nullptr;
+    trs_event done = nullptr;
+};
+std::map<int, Ingress>& g_ingress = *new std::map<int, Ingress>();
+}  // namespace
+
 TensorP from_host(const float* data, const Shape& shape, int device, bool pinned) {
     for (i64 d : shape) if (d < 0) throw Error(ErrKind::InvalidArgument, "negative dimension");
     const i64 n = element_count(shape);
+    if (n > 0 && pinned) {
+        Ingress& in = g_ingress[device];
+        if (!in.stream) {
+            check_cuda(trs_stream_create(device, &in.stream), "creating the upload stream");
+            check_cuda(trs_event_create(&in.done), "creating the upload event");
+        }
+        // The block is taken in the upload stream's order: if the compute stream freed it with work still queued, the
+        // copy waits for exactly that work (not for what the compute stream was given afterwards).
+        auto st = std::make_shared<Storage>();
+        st->device = device;
+        st->count = n;
+        st->ptr = alloc_floats_on(n, device, in.stream);
+        check_cuda(trs_memcpy_h2d(st->ptr, data, (size_t)n * sizeof(float), in.stream), "host to device copy");
+        check_cuda(trs_event_record(in.done, in.stream), "upload event");
+        check_cuda(trs_stream_wait_event(stream_for(device), in.done), "ordering kernels behind the upload");
+        return make_tensor(View{st, shape, contiguous_strides(shape), 0});
+    }
     auto st = alloc_storage(n, device);
     if (n > 0) {
         trs_stream s = stream_for(device);
         check_cuda(trs_memcpy_h2d(st->ptr, data, (size_t)n * sizeof(float), s), "host to device copy");
-        // A pageable source may be released by the caller at once; a pinned source is promised to
-        // stay untouched until the stream reaches the copy, so the call returns without waiting.
-        if (!pinned) check_cuda(trs_stream_sync(s), "host to device copy");
+        check_cuda(trs_stream_sync(s), "host to device copy");      // a pageable source may be released by the caller at once
     }
     return make_tensor(View{st, shape, contiguous_strides(shape), 0});
 }

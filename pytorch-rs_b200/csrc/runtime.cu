@@ -23,11 +23,13 @@ constexpr int kMaxDevices = 16;
 struct FreeBlock {
     void* ptr;
     trs_stream last;       // stream whose queued work may still touch the block; NULL when nothing can
+    cudaEvent_t freed;     // recorded on `last` when the block was handed back: everything that may touch it lies before
 };
 struct DeviceCache {
     std::mutex mu;
     std::multimap<size_t, FreeBlock> free_blocks;      // rounded size -> block
     std::unordered_map<void*, size_t> live;            // block -> rounded size
+    std::vector<cudaEvent_t> spare_events;             // events of this device waiting for their next block
     int64_t in_use = 0, reserved = 0;
     int sms = 0;
 };
@@ -42,9 +44,23 @@ size_t round_size(size_t bytes) {
 void release_all(DeviceCache& c) {
     for (auto& kv : c.free_blocks) {
         cudaFree(kv.second.ptr);                          // cudaFree waits for the device to finish using the block
+        if (kv.second.freed) c.spare_events.push_back(kv.second.freed);
         c.reserved -= (int64_t)kv.first;
     }
     c.free_blocks.clear();
+}
+
+// Events are pooled: one is needed per free, and creating one costs as much as the free itself.  Caller holds c.mu and
+// has the device selected.
+cudaEvent_t take_event(DeviceCache& c) {
+    if (!c.spare_events.empty()) {
+        cudaEvent_t e = c.spare_events.back();
+        c.spare_events.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return e;
 }
 }  // namespace
 
@@ -110,18 +126,16 @@ static int32_t cache_malloc(int32_t device, size_t bytes, trs_stream stream, voi
     for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
         FreeBlock& b = it->second;
         if (b.last != nullptr && b.last != stream) {
-            if (stream) {
-                // order the new user behind everything the previous stream has queued (which includes its use of the block)
-                cudaEvent_t ev;
-                if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); continue; }
-                const bool ok = cudaEventRecord(ev, b.last->stream) == cudaSuccess && cudaStreamWaitEvent(stream->stream, ev, 0) == cudaSuccess;
-                cudaEventDestroy(ev);
-                if (!ok) { cudaGetLastError(); continue; }
-            } else if (cudaStreamQuery(b.last->stream) != cudaSuccess) {
+            if (stream && b.freed) {
+                // order the new user behind the work that was queued on the other stream when the block was freed
+                // (and no further: later work of that stream cannot touch a block it had already given up)
+                if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
+            } else if (b.freed ? cudaEventQuery(b.freed) != cudaSuccess : cudaStreamQuery(b.last->stream) != cudaSuccess) {
                 cudaGetLastError();
                 continue;                                   // still busy: leave it for its own stream
             }
         }
+        if (b.freed) c.spare_events.push_back(b.freed);       // a wait already enqueued keeps the state it saw
         *ptr = b.ptr;
         c.live[*ptr] = it->first;
         c.in_use += (int64_t)it->first;
@@ -154,7 +168,16 @@ static int32_t cache_free(int32_t device, void* ptr, trs_stream stream) {
     auto it = c.live.find(ptr);
     if (it == c.live.end()) return fail(TRS_ERR_INVALID_ARGUMENT, "pointer was not allocated by trs_malloc on device %d", device);
     c.in_use -= (int64_t)it->second;
-    c.free_blocks.emplace(it->second, FreeBlock{ptr, stream});
+    cudaEvent_t freed = nullptr;
+    if (stream) {
+        DeviceGuard guard(device);
+        if (guard.ok && (freed = take_event(c)) != nullptr && cudaEventRecord(freed, stream->stream) != cudaSuccess) {
+            cudaGetLastError();
+            c.spare_events.push_back(freed);
+            freed = nullptr;                                // falls back to querying the stream itself
+        }
+    }
+    c.free_blocks.emplace(it->second, FreeBlock{ptr, stream, freed});
     c.live.erase(it);
     return TRS_OK;
 }
@@ -163,7 +186,11 @@ static int32_t cache_free(int32_t device, void* ptr, trs_stream stream) {
 static void forget_stream(trs_stream stream) {
     DeviceCache& c = g_cache[stream->device];
     std::lock_guard<std::mutex> lock(c.mu);
-    for (auto& kv : c.free_blocks) if (kv.second.last == stream) kv.second.last = nullptr;
+    for (auto& kv : c.free_blocks)
+        if (kv.second.last == stream) {
+            kv.second.last = nullptr;
+            if (kv.second.freed) { c.spare_events.push_back(kv.second.freed); kv.second.freed = nullptr; }
+        }
 }
 
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr) { return cache_malloc(device, bytes, nullptr, ptr); }

@@ -497,3 +497,26 @@ def test_deep_chains_are_released_and_differentiated_without_recursion():
     detached = z.detach()
     del z
     assert detached.tolist() == [1.5, -2.0]
+
+
+def test_pinned_uploads_on_their_own_stream_respect_recycled_blocks():
+    """Uploads from page-locked memory run on an upload stream, beside the kernels.  A block that the compute stream
+    has just given up (with kernels that read it still queued) may be handed to the next upload: the copy must wait
+    for exactly those kernels, and kernels must wait for the copy they read."""
+    n = 1 << 20
+    stage = [torch.pinned_empty(n), torch.pinned_empty(n)]
+    outs = [torch.pinned_empty(n) for _ in range(6)]
+    held = None
+    for i in range(6):
+        buf = stage[i % 2]
+        buf[...] = np.arange(n, dtype=np.float32) + i
+        x = torch.tensor(buf, device=DEV)              # same size every time: the cache recycles the previous block
+        y = (x * 2.0 + 1.0).relu()
+        y.copy_to_host(outs[i], non_blocking=True)
+        held = y                                         # x is dropped here with its readers still queued
+        del x
+    torch.synchronize(0)
+    for i in range(6):
+        assert np.array_equal(outs[i], (np.arange(n, dtype=np.float32) + i) * 2.0 + 1.0), i
+    for array in stage + outs:
+        torch.pinned_free(array)
