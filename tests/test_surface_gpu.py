@@ -504,11 +504,11 @@ def test_pinned_uploads_on_their_own_stream_respect_recycled_blocks():
     has just given up (with kernels that read it still queued) may be handed to the next upload: the copy must wait
     for exactly those kernels, and kernels must wait for the copy they read."""
     n = 1 << 20
-    stage = [torch.pinned_empty(n), torch.pinned_empty(n)]
+    stage = [torch.pinned_empty(n) for _ in range(6)]       # a source stays untouched until its copy has run
     outs = [torch.pinned_empty(n) for _ in range(6)]
     held = None
     for i in range(6):
-        buf = stage[i % 2]
+        buf = stage[i]
         buf[...] = np.arange(n, dtype=np.float32) + i
         x = torch.tensor(buf, device=DEV)              # same size every time: the cache recycles the previous block
         y = (x * 2.0 + 1.0).relu()
