@@ -37,7 +37,10 @@ const char* trsh_last_error(void);
 /* creation / egress: Tensor::from_vec, zeros/ones/full (src/tensor.rs:302-423), try_to_vec, item (2438) */
 int32_t trsh_from_host(const float* data, int32_t rank, const int64_t* shape, int32_t device, trsh_tensor* out);
 /* Same, for page-locked host memory (trs_malloc_host): returns once the copy is enqueued; the caller
- * keeps the source unchanged until the device stream has passed it (trsh_sync or a later read-back). */
+ * keeps the source unchanged until the device stream has passed it (trsh_sync or a later read-back).
+ * The copy runs on an upload stream of its own: it proceeds while kernels queued earlier are still
+ * running, and only kernels that come after this call wait for it -- a host that creates the next
+ * batch's tensor before it waits for the current result overlaps the upload with the computation. */
 int32_t trsh_from_pinned_host(const float* data, int32_t rank, const int64_t* shape, int32_t device, trsh_tensor* out);
 int32_t trsh_full(int32_t rank, const int64_t* shape, float value, int32_t device, trsh_tensor* out);
 int32_t trsh_to_host(trsh_tensor t, float* out);          /* logical row-major order, numel floats */

@@ -123,24 +123,30 @@ static int32_t cache_malloc(int32_t device, size_t bytes, trs_stream stream, voi
     DeviceGuard guard(device);
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     // Reuse only a block that wastes at most 1/8 of itself, so large blocks stay available for large requests.
-    for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
-        FreeBlock& b = it->second;
-        if (b.last != nullptr && b.last != stream) {
-            if (stream && b.freed) {
-                // order the new user behind the work that was queued on the other stream when the block was freed
-                // (and no further: later work of that stream cannot touch a block it had already given up)
-                if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
-            } else if (b.freed ? cudaEventQuery(b.freed) != cudaSuccess : cudaStreamQuery(b.last->stream) != cudaSuccess) {
-                cudaGetLastError();
-                continue;                                   // still busy: leave it for its own stream
+    // First choice: a block the requesting stream freed itself, or one nothing can touch any more.  Second choice
+    // (only for a request that names a stream): a block another stream gave up with work still queued -- the
+    // requester is then ordered behind that work, which costs it the wait.
+    for (int pass = 0; pass < 2; ++pass) {
+        for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
+            FreeBlock& b = it->second;
+            if (b.last != nullptr && b.last != stream) {
+                const bool idle = b.freed ? cudaEventQuery(b.freed) == cudaSuccess : cudaStreamQuery(b.last->stream) == cudaSuccess;
+                if (!idle) {
+                    cudaGetLastError();
+                    if (pass == 0 || !stream || !b.freed) continue;
+                    // order the new user behind the work that was queued on the other stream when the block was freed
+                    // (and no further: later work of that stream cannot touch a block it had already given up)
+                    if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
+                }
             }
+            if (b.freed) c.spare_events.push_back(b.freed);       // a wait already enqueued keeps the state it saw
+            *ptr = b.ptr;
+            c.live[*ptr] = it->first;
+            c.in_use += (int64_t)it->first;
+            c.free_blocks.erase(it);
+            return TRS_OK;
         }
-        if (b.freed) c.spare_events.push_back(b.freed);       // a wait already enqueued keeps the state it saw
-        *ptr = b.ptr;
-        c.live[*ptr] = it->first;
-        c.in_use += (int64_t)it->first;
-        c.free_blocks.erase(it);
-        return TRS_OK;
+        if (!stream) break;
     }
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, rounded);
