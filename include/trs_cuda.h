@@ -149,10 +149,12 @@ int32_t trs_device_pci_bus_id(int32_t device, char* buffer, int32_t length);
 int32_t trs_malloc(int32_t device, size_t bytes, void** ptr);       /* cached blocks; Storage::from_owned */
 int32_t trs_free(int32_t device, void* ptr);                        /* Storage drop */
 /* Stream-ordered forms.  trs_free_async hands the block back while work that uses it may still be queued on
- * `stream`; the cache remembers that stream.  trs_malloc_async may return such a block at once to the same
- * stream (stream order protects it); for any other stream it first makes that stream wait for the work the
- * freeing stream had queued.  Plain trs_malloc only returns a remembered block once its stream has drained,
- * and plain trs_free states that nothing queued anywhere still uses the block. */
+ * `stream`; the cache remembers that stream and an event recorded on it at that moment.  trs_malloc_async returns
+ * such a block at once to the same stream (stream order protects it).  Another stream gets a block nothing can touch
+ * any more, else new memory (so that, say, an upload stream is never queued behind the kernels it should overlap),
+ * and only when memory is short a block that is still in use, behind the work its stream had queued when it was
+ * freed.  Plain trs_malloc only returns a remembered block once that work has finished, and plain trs_free states
+ * that nothing queued anywhere still uses the block. */
 int32_t trs_malloc_async(int32_t device, size_t bytes, trs_stream stream, void** ptr);
 int32_t trs_free_async(int32_t device, void* ptr, trs_stream stream);
 int32_t trs_empty_cache(int32_t device);

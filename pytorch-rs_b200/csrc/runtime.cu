@@ -123,33 +123,42 @@ static int32_t cache_malloc(int32_t device, size_t bytes, trs_stream stream, voi
     DeviceGuard guard(device);
     if (!guard.ok) return fail(TRS_ERR_NO_DEVICE, "cannot select CUDA device %d", device);
     // Reuse only a block that wastes at most 1/8 of itself, so large blocks stay available for large requests.
-    // First choice: a block the requesting stream freed itself, or one nothing can touch any more.  Second choice
-    // (only for a request that names a stream): a block another stream gave up with work still queued -- the
-    // requester is then ordered behind that work, which costs it the wait.
-    for (int pass = 0; pass < 2; ++pass) {
-        for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
-            FreeBlock& b = it->second;
-            if (b.last != nullptr && b.last != stream) {
-                const bool idle = b.freed ? cudaEventQuery(b.freed) == cudaSuccess : cudaStreamQuery(b.last->stream) == cudaSuccess;
-                if (!idle) {
-                    cudaGetLastError();
-                    if (pass == 0 || !stream || !b.freed) continue;
-                    // order the new user behind the work that was queued on the other stream when the block was freed
-                    // (and no further: later work of that stream cannot touch a block it had already given up)
-                    if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
-                }
-            }
-            if (b.freed) c.spare_events.push_back(b.freed);       // a wait already enqueued keeps the state it saw
-            *ptr = b.ptr;
-            c.live[*ptr] = it->first;
-            c.in_use += (int64_t)it->first;
-            c.free_blocks.erase(it);
-            return TRS_OK;
+    // First choice: a block the requesting stream freed itself, or one nothing can touch any more.
+    auto take = [&](std::multimap<size_t, FreeBlock>::iterator it) {
+        FreeBlock& b = it->second;
+        if (b.freed) c.spare_events.push_back(b.freed);       // a wait already enqueued keeps the state it saw
+        *ptr = b.ptr;
+        c.live[*ptr] = it->first;
+        c.in_use += (int64_t)it->first;
+        c.free_blocks.erase(it);
+    };
+    bool busy_candidates = false;
+    for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
+        FreeBlock& b = it->second;
+        if (b.last != nullptr && b.last != stream) {
+            const bool idle = b.freed ? cudaEventQuery(b.freed) == cudaSuccess : cudaStreamQuery(b.last->stream) == cudaSuccess;
+            if (!idle) { cudaGetLastError(); busy_candidates = true; continue; }
         }
-        if (!stream) break;
+        take(it);
+        return TRS_OK;
     }
+    // Second choice: new memory.  Only blocks that another stream gave up with work still queued are left; taking one
+    // would order the requester behind that work (an upload behind the kernels it is meant to overlap), whereas one
+    // more block in the pool gives every later request of this kind an idle one.
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, rounded);
+    if (e == cudaErrorMemoryAllocation && stream && busy_candidates) {
+        // Third choice, when memory is short: such a block after all, behind the work that was queued on the other
+        // stream when it was freed (and no further: later work of that stream cannot touch a block it had given up).
+        cudaGetLastError();
+        for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
+            FreeBlock& b = it->second;
+            if (!b.freed || b.last == nullptr || b.last == stream) continue;
+            if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
+            take(it);
+            return TRS_OK;
+        }
+    }
     if (e == cudaErrorMemoryAllocation) {
         cudaGetLastError();
         release_all(c);                      // give cached blocks back and retry once
