@@ -150,6 +150,14 @@ def headline_config(world):
             "parallelism": f"dp{world}", "algorithmic_bytes_per_step_per_gpu": ALGO_BYTES}
 
 
+def reference_rows(total_steps):
+    """Physical rows of x per step of the reference arm.  One full-size step takes about 6 s on one core: the whole
+    workload while the run fits in ~2.5 minutes, else as many of its 8192 rows (a multiple of 256) as keep it near 2."""
+    if total_steps * 6.0 <= 160:
+        return N_SIDE
+    return max(256, min(N_SIDE, int(N_SIDE * 120.0 / (total_steps * 6.0)) // 256 * 256))
+
+
 def run_reference(args, rank, world):
     """Reference arm: the reference's CPU algorithm for this chain (C++ restatement in oracle/, since
     no Rust toolchain exists to build the original) on the host cores; single-threaded, as the
@@ -158,10 +166,7 @@ def run_reference(args, rank, world):
         return
     from oracle import ref
     ref.build()
-    total_steps = args.steps + args.warmup
-    # one full-size step takes about 6 s on one core: the whole workload while the run fits in ~2.5 minutes, else as
-    # many of its 8192 physical rows (a multiple of 256) as keep it near 2 minutes
-    rows = N_SIDE if total_steps * 6.0 <= 160 else max(256, min(N_SIDE, int(N_SIDE * 120.0 / (total_steps * 6.0)) // 256 * 256))
+    rows = reference_rows(args.steps + args.warmup)
     xs, b = make_inputs(0, rows)
     bytes_per_step = 8 * rows * N_SIDE + 4 * rows
     for _ in range(args.warmup):
@@ -194,6 +199,7 @@ class Bench:
         from torch_rs._device import Stream
         self.torch, self.tdist = torch, tdist
         self.rank, self.world, self.local_rank = rank, world, local_rank
+        self.shards = world          # how many shards the strong-scaled workloads are cut into (--shard-of overrides it)
         self.dev = f"cuda:{local_rank}"
         from torch_rs import _abi
         _abi.check(_abi.lib().trs_set_current_device(local_rank))      # pinned staging memory belongs to this rank's GPU context
@@ -484,7 +490,7 @@ def run_c3(bench, args):
     rng = np.random.default_rng(0)
     a = (rng.standard_normal((n, n)) / 64).astype(np.float32)
     b = (rng.standard_normal((n, n)) / 64).astype(np.float32)
-    lo, hi = bench.tdist.shard_bounds(n, rank, world)
+    lo, hi = bench.tdist.shard_bounds(n, rank, bench.shards)
     A, B = torch.tensor(a[lo:hi], device=dev), torch.tensor(b, device=dev)
     held = [None]
 
@@ -566,7 +572,7 @@ def run_c3(bench, args):
 def run_c4(bench, args):
     """relu(X @ W.mT + bias), 64 batches of 1024^3; batches sharded over the ranks, no collective."""
     torch, dev, rank, world = bench.torch, bench.dev, bench.rank, bench.world
-    lo, hi = bench.tdist.shard_bounds(64, rank, world)
+    lo, hi = bench.tdist.shard_bounds(64, rank, bench.shards)
     nb = hi - lo
     rng = np.random.default_rng(rank)
     x = rng.standard_normal((nb, 1024, 1024), dtype=np.float32)
@@ -660,7 +666,7 @@ def run_c5(bench, args):
     all-reduce of the three gradients inside the step (each one as soon as its kernel has finished)."""
     torch, dev, rank, world, tdist = bench.torch, bench.dev, bench.rank, bench.world, bench.tdist
     total_rows = 65536
-    lo, hi = tdist.shard_bounds(total_rows, rank, world)
+    lo, hi = tdist.shard_bounds(total_rows, rank, bench.shards)
     rows = hi - lo
     x = np.random.default_rng(1000 + rank).standard_normal((rows, 4096), dtype=np.float32)
     shared = np.random.default_rng(0)
@@ -777,6 +783,8 @@ SIDE = {"c1": lambda bench, args: run_c1(bench), "t1": lambda bench, args: run_t
 
 def run_ours(args, rank, world, local_rank):
     bench = Bench(rank, world, local_rank)
+    if args.shard_of:
+        bench.shards = args.shard_of
     torch = bench.torch
     if args.workload != "c2":
         result = SIDE[args.workload](bench, args)
@@ -834,6 +842,9 @@ def main():
                          "any other value runs that workload alone")
     ap.add_argument("--min-seconds", type=float, default=MIN_REGION_SECONDS,
                     help="shortest timed region of a side workload (a profiler run wants it short)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="profiling aid for one GPU: size configs 3/4/5 as rank 0's shard of a job of this many ranks "
+                         "(the aggregate figures of such a run mean nothing; the per-step time is one rank's)")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the copy ceiling and configs 1, 3, 4, 5")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
