@@ -800,8 +800,14 @@ def run_ours(args, rank, world, local_rank):
     if not args.no_extra:
         extra["copy"] = run_copy_ceiling(bench)
         for name in ("c1", "c3", "c4", "c5"):
-            extra[name] = SIDE[name](bench, args)
-            torch.synchronize(local_rank)
+            # a side workload that fails must not take the headline with it: its entry then carries the error
+            try:
+                extra[name] = SIDE[name](bench, args)
+                torch.synchronize(local_rank)
+            except Exception as err:                                  # noqa: BLE001 - reported, not swallowed
+                import traceback
+                traceback.print_exc()
+                extra[name] = {"error": f"{type(err).__name__}: {err}"[:600]}
     bench.barrier()
     if world > 1:
         bench.tdist.destroy_process_group()

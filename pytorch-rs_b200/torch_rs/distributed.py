@@ -52,7 +52,9 @@ def init_process_group(backend: str | None = None) -> str:
     if backend not in ("nccl", "gloo"):
         raise ValueError(f"unknown backend {backend!r}")
     if not dist.is_initialized():
-        dist.init_process_group("gloo")
+        import datetime
+        # control-plane operations are small; a rank that died is noticed within this time instead of the default half hour
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=float(os.environ.get("TRS_CONTROL_TIMEOUT_S", "600"))))
     _state.update(initialized=True, backend=backend)
     if backend == "nccl":
         from . import _abi
