@@ -400,6 +400,54 @@ def run_headline(bench, args):
     }
 
 
+# ---- the backward pass's streaming kernels -------------------------------------------------------------
+
+def run_backward_kernels(bench):
+    """The kernels a backward pass runs besides GEMMs, each alone through the C ABI on 1 GiB operands (larger than
+    L2), against the HBM roofline: the relu VJP as a fused chain (read the saved input and the upstream, write the
+    gradient: 12 B per element), the column sum that un-broadcasts a bias gradient (db1 = sum over rows of dZ: 4 B per
+    element), the full sum of a loss (4 B per element) and the in-place accumulation of a leaf gradient (12 B per
+    element).  Per GPU, rank 0's figures."""
+    from torch_rs import _abi
+    from torch_rs._device import DeviceBuffer, Event, Stream
+    lib = _abi.lib()
+    dev = bench.local_rank
+    rows, cols = 65536, 4096
+    n = rows * cols
+    stream = Stream(dev)
+    z, g, out = DeviceBuffer(n, dev), DeviceBuffer(n, dev), DeviceBuffer(n, dev)
+    small = DeviceBuffer(cols, dev)
+    _abi.check(lib.trs_fill_f32(z.ptr, n, ctypes.c_float(0.5), stream.handle))
+    _abi.check(lib.trs_fill_f32(g.ptr, n, ctypes.c_float(0.25), stream.handle))
+    _abi.check(lib.trs_fill_f32(out.ptr, n, ctypes.c_float(0.0), stream.handle))
+    prog = _abi.make_program(2, [("relu_vjp", 0, 1, 0)], [2])
+    ins = (_abi.Operand * 2)(_abi.make_operand(z.ptr, 0, [rows, cols], [cols, 1]), _abi.make_operand(g.ptr, 0, [rows, cols], [cols, 1]))
+    outs = (_abi.Operand * 1)(_abi.make_operand(out.ptr, 0, [rows, cols], [cols, 1]))
+    whole = _abi.make_operand(z.ptr, 0, [rows, cols], [cols, 1])
+    cases = {
+        "relu_vjp_chain": (12 * n, lambda: _abi.check(lib.trs_pointwise(prog, ins, outs, stream.handle))),
+        "column_sum_unbroadcast": (4 * n, lambda: _abi.check(lib.trs_unbroadcast_sum_f32(g.ptr, rows, cols, 0, small.ptr, stream.handle))),
+        "full_sum": (4 * n, lambda: _abi.check(lib.trs_reduce_sum_f32(ctypes.byref(whole), small.ptr, stream.handle))),
+        "leaf_gradient_accumulate": (12 * n, lambda: _abi.check(lib.trs_accumulate_f32(out.ptr, g.ptr, n, stream.handle))),
+    }
+    result = {"operand": "f32 [65536, 4096] (1 GiB) each", "peak_gbs": bench.hbm_peak, "peak_source": f"of {bench.peak_kind}"}
+    for name, (nbytes, call) in cases.items():
+        for _ in range(3):
+            call()
+        stream.sync()
+        e0, e1 = Event(), Event()
+        e0.record(stream)
+        reps = 20
+        for _ in range(reps):
+            call()
+        e1.record(stream)
+        e1.sync()
+        ms = e0.elapsed_ms(e1) / reps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        result[name] = {"GB/s": gbs, "ms": ms, "algorithmic_bytes": nbytes, "frac": gbs / bench.hbm_peak}
+    return result
+
+
 # ---- host <-> device copy ceiling ---------------------------------------------------------------------
 
 def run_copy_ceiling(bench, mib=256, reps=5):
@@ -778,7 +826,7 @@ def run_c5(bench, args):
 
 
 SIDE = {"c1": lambda bench, args: run_c1(bench), "t1": lambda bench, args: run_t1(bench), "c3": run_c3, "c4": run_c4, "c5": run_c5,
-        "copy": lambda bench, args: run_copy_ceiling(bench)}
+        "copy": lambda bench, args: run_copy_ceiling(bench), "bwd": lambda bench, args: run_backward_kernels(bench)}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -799,6 +847,11 @@ def run_ours(args, rank, world, local_rank):
     extra = {}
     if not args.no_extra:
         extra["copy"] = run_copy_ceiling(bench)
+        if rank == 0:
+            try:
+                extra["backward_kernels"] = run_backward_kernels(bench)
+            except Exception as err:                                  # noqa: BLE001 - reported, not swallowed
+                extra["backward_kernels"] = {"error": f"{type(err).__name__}: {err}"[:600]}
         for name in ("c1", "c3", "c4", "c5"):
             # a side workload that fails must not take the headline with it: its entry then carries the error
             try:
@@ -843,7 +896,7 @@ def main():
     ap.add_argument("--regions", type=int, default=9, help="timed regions of `steps` steps each for the headline; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-slabs", type=int, default=8, help="row slabs per end-to-end step (must divide 8192)")
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "t1", "c3", "c4", "c5", "copy"],
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "t1", "c3", "c4", "c5", "copy", "bwd"],
                     help="c2 (default) is the headline fused chain with every other configuration under `extra`; "
                          "any other value runs that workload alone")
     ap.add_argument("--min-seconds", type=float, default=MIN_REGION_SECONDS,
