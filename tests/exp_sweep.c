@@ -59,6 +59,11 @@ static long long ulp_distance(float a, float b) {
     return d < 0 ? -d : d;
 }
 
+/* The twin over an array, for the GPU test that compares the device function with it bit for bit. */
+void exp_twin_array(const float* x, float* y, long long n) {
+    for (long long i = 0; i < n; ++i) y[i] = exp_twin(x[i]);
+}
+
 int main(int argc, char** argv) {
     const uint32_t stride = argc > 1 ? (uint32_t)strtoul(argv[1], 0, 10) : 64;
     const uint32_t ranges[2][2] = {{0u, as_bits(89.5f)}, {0x80000000u, as_bits(-104.5f)}};

@@ -194,3 +194,28 @@ def test_special_values_bitwise():
         expected = x.binary(op, y)
         (got,) = run_pointwise([(op, 0, 1, 0)], [2], [x, y], [(expected.shape, expected.strides)])
         assert_bits_equal(got, expected.storage, op)
+
+
+def test_device_exp_equals_its_cpu_twin_bit_for_bit(tmp_path):
+    """tests/exp_sweep.c restates the device exp operation for operation; on the host it has been swept against
+    glibc expf over every float32 input.  Here the device function is compared with that twin bit for bit on every
+    997th float32 bit pattern of the whole number line plus the patterns around the path's thresholds, so the sweep's
+    bound (1 ulp from glibc) carries over to what the GPU computes -- nothing was contracted or reordered on the way."""
+    import ctypes
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_path = tmp_path / "libexp_twin.so"
+    subprocess.check_call(["gcc", "-O2", "-shared", "-fPIC", "-o", str(lib_path), os.path.join(root, "tests", "exp_sweep.c"), "-lm"])
+    twin = ctypes.CDLL(str(lib_path))
+    bits = np.arange(0, 1 << 32, 997, dtype=np.uint64).astype(np.uint32)
+    edges = np.concatenate([np.array([v], dtype=np.float32).view(np.uint32).astype(np.int64) + np.arange(-64, 65)
+                            for v in (87.0, -87.0, 88.72284, -103.97208, 0.0, -0.0, 1.0, -1.0, 90.0, -110.0)]).astype(np.uint32)
+    x = np.concatenate([bits, edges]).view(np.float32)
+    want = np.empty_like(x)
+    twin.exp_twin_array(x.ctypes.data_as(ctypes.c_void_p), want.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(x.size))
+    t = RefTensor.from_numpy(x)
+    (got,) = run_pointwise([("exp", 0, 0, 0)], [1], [t], [(t.shape, t.strides)])
+    finite = ~np.isnan(want)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[finite].view(np.uint32), want[finite].view(np.uint32))
