@@ -588,8 +588,8 @@ def run_c3(bench, args):
     def step_e2e():
         Ad, Bd = upcoming[0]
         product = torch.matmul(Ad, Bd).materialize()
-        upcoming[0] = (torch.tensor(a_host, device=dev), torch.tensor(b_host, device=dev))     # next operands upload under this product
-        product.copy_to_host(c_host, non_blocking=True)
+        product.copy_to_host(c_host, non_blocking=True)       # ordered behind the product only: issued before the next upload
+        upcoming[0] = (torch.tensor(a_host, device=dev), torch.tensor(b_host, device=dev))     # uploads under this product and its read-back
         torch.synchronize(bench.local_rank)
     e2e_ms = bench.time_wall(step_e2e, 5)
     upcoming.clear()
@@ -788,9 +788,9 @@ def run_c5(bench, args):
     def step_e2e():
         loss, params = mlp_step(torch, upcoming[0], w1, w2, b1)
         tdist.all_reduce_gradients(params)
-        upcoming[0] = torch.tensor(x_host, device=dev)
         for p, dst in zip(params, g_host):
-            p.grad.copy_to_host(dst, non_blocking=True)
+            p.grad.copy_to_host(dst, non_blocking=True)       # ordered behind the gradients only: issued before the next upload
+        upcoming[0] = torch.tensor(x_host, device=dev)
         held[0] = loss.item()
         torch.synchronize(bench.local_rank)
     e2e_ms = bench.time_wall(step_e2e, 3, warmup=1)
