@@ -13,9 +13,10 @@ every rank runs the same-sized shard of an N-times larger batch (weak scaling, n
 Algorithmic bytes per step and GPU: 8 B per element (x read once, result written once) + b
 = 8*8192*8192 + 4*8192 = 536,903,680 B.
 
-`extra` carries the metric's other half, each with its own roofline, clock record, end-to-end figure and
-(at N=1) CPU baseline: c3 matmul 4096^3, c4 bmm 64x1024^3 + bias + relu (batches sharded over the ranks),
-c5 two-layer MLP forward+backward on 65,536 rows (rows sharded over the ranks, NCCL all-reduce of the
+`extra` carries the rest: c1 relu(x+y) and t1 x.mT+y (the staged-tile kernel class) as further pointwise figures,
+the streaming kernels of a backward pass, the host-link copy ceiling, and the metric's other half, each with its
+own roofline, clock record, end-to-end figure and (at N=1) CPU baseline: c3 matmul 4096^3, c4 bmm 64x1024^3 + bias
++ relu (batches sharded over the ranks), c5 two-layer MLP forward+backward on 65,536 rows (rows sharded over the ranks, NCCL all-reduce of the
 W1/W2/b1 gradients inside the step) -- those three strong-scaled: the total work is fixed as N grows.
 Prints ONE JSON line (rank 0).
 """
@@ -852,7 +853,7 @@ def run_ours(args, rank, world, local_rank):
                 extra["backward_kernels"] = run_backward_kernels(bench)
             except Exception as err:                                  # noqa: BLE001 - reported, not swallowed
                 extra["backward_kernels"] = {"error": f"{type(err).__name__}: {err}"[:600]}
-        for name in ("c1", "c3", "c4", "c5"):
+        for name in ("c1", "t1", "c3", "c4", "c5"):
             # a side workload that fails must not take the headline with it: its entry then carries the error
             try:
                 extra[name] = SIDE[name](bench, args)
