@@ -152,8 +152,9 @@ int32_t trs_free(int32_t device, void* ptr);                        /* Storage d
  * `stream`; the cache remembers that stream and an event recorded on it at that moment.  trs_malloc_async returns
  * such a block at once to the same stream (stream order protects it).  Another stream gets a block nothing can touch
  * any more, else new memory (so that, say, an upload stream is never queued behind the kernels it should overlap),
- * and only when memory is short a block that is still in use, behind the work its stream had queued when it was
- * freed.  Plain trs_malloc only returns a remembered block once that work has finished, and plain trs_free states
+ * and a block that is still in use -- the one freed longest ago, behind the work its stream had queued when it
+ * was freed -- only once eight such blocks are waiting (a loop that never drains must not grow the pool without
+ * bound) or when memory is short.  Plain trs_malloc only returns a remembered block once that work has finished, and plain trs_free states
  * that nothing queued anywhere still uses the block. */
 int32_t trs_malloc_async(int32_t device, size_t bytes, trs_stream stream, void** ptr);
 int32_t trs_free_async(int32_t device, void* ptr, trs_stream stream);

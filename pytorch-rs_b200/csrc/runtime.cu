@@ -132,32 +132,39 @@ static int32_t cache_malloc(int32_t device, size_t bytes, trs_stream stream, voi
         c.in_use += (int64_t)it->first;
         c.free_blocks.erase(it);
     };
-    bool busy_candidates = false;
+    int busy_candidates = 0;
     for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
         FreeBlock& b = it->second;
         if (b.last != nullptr && b.last != stream) {
             const bool idle = b.freed ? cudaEventQuery(b.freed) == cudaSuccess : cudaStreamQuery(b.last->stream) == cudaSuccess;
-            if (!idle) { cudaGetLastError(); busy_candidates = true; continue; }
+            if (!idle) { cudaGetLastError(); ++busy_candidates; continue; }
         }
         take(it);
         return TRS_OK;
     }
     // Second choice: new memory.  Only blocks that another stream gave up with work still queued are left; taking one
     // would order the requester behind that work (an upload behind the kernels it is meant to overlap), whereas one
-    // more block in the pool gives every later request of this kind an idle one.
-    void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, rounded);
-    if (e == cudaErrorMemoryAllocation && stream && busy_candidates) {
-        // Third choice, when memory is short: such a block after all, behind the work that was queued on the other
-        // stream when it was freed (and no further: later work of that stream cannot touch a block it had given up).
-        cudaGetLastError();
+    // more block in the pool gives every later request of this kind an idle one.  The pool must not grow without
+    // bound in a loop that never drains, though: once kMaxBusyCandidates such blocks are waiting, the oldest of them
+    // (freed first, so its work finishes first) is taken instead, behind the work that was queued on the other stream
+    // when it was freed (and no further: later work of that stream cannot touch a block it had given up).
+    constexpr int kMaxBusyCandidates = 8;
+    auto take_busy = [&]() {
         for (auto it = c.free_blocks.lower_bound(rounded); it != c.free_blocks.end() && it->first <= rounded + rounded / 8; ++it) {
             FreeBlock& b = it->second;
             if (!b.freed || b.last == nullptr || b.last == stream) continue;
             if (cudaStreamWaitEvent(stream->stream, b.freed, 0) != cudaSuccess) { cudaGetLastError(); continue; }
             take(it);
-            return TRS_OK;
+            return true;
         }
+        return false;
+    };
+    if (stream && busy_candidates >= kMaxBusyCandidates && take_busy()) return TRS_OK;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, rounded);
+    if (e == cudaErrorMemoryAllocation && stream && busy_candidates > 0) {
+        cudaGetLastError();                  // memory is short: such a block after all
+        if (take_busy()) return TRS_OK;
     }
     if (e == cudaErrorMemoryAllocation) {
         cudaGetLastError();
